@@ -1,0 +1,19 @@
+"""B200-native (sm_100a) replacement of DA-Transformer's ``fs_plugins/custom_ops``.
+
+Re-exports the names of ``fs_plugins/custom_ops/__init__.py`` so that
+``from da_transformer_b200 import dag_loss, dag_best_alignment,
+dag_logsoftmax_gather_inplace`` is a drop-in for the reference import.
+"""
+from .dag_loss import (  # noqa: F401
+    DagBestAlignmentFunc,
+    DagLogsoftmaxGatherFunc,
+    DagLossFunc,
+    dag_best_alignment,
+    dag_logsoftmax_gather_inplace,
+    dag_loss,
+    get_dag_kernel,
+    last_status,
+    logsoftmax_gather,
+)
+
+__version__ = "0.1.0"

@@ -1,0 +1,105 @@
+// Work decomposition shared by the alpha sweep and the best-alignment sweep.
+//
+// In window coordinates (see dag_sweep.cu) every step reduces, for each column c, over the
+// rows r of the triangle { 0 <= r <= c < W, c - r < K }.  The triangle is cut into tiles of
+// 32 rows x 32 columns, enumerated column-block major, and the enumeration is split into
+// contiguous ranges of (almost) equal length, one per warp.  A warp keeps one accumulator
+// per lane (= column) while it walks the tiles of a column block; a column block shared by
+// several warps is merged through shared memory.
+#pragma once
+
+#include "dat_common.cuh"
+
+namespace dat {
+
+constexpr int kSweepThreads = 512;
+constexpr int kSweepWarps = kSweepThreads / 32;
+constexpr int kChunk = 8;
+
+__host__ __device__ inline bool lengths_valid(long long ol, long long tl, int T, int L) {
+    return tl >= 2 && ol >= 2 && ol >= tl && ol <= L && tl <= T;
+}
+
+struct SweepSmem {
+    float *row[2];      // recursion rows, indexed by absolute vertex
+    float *fin_m;       // per window column: merged running max / sum
+    float *fin_s;
+    float *part;        // [2][warps][2][32] partial (m, s) of column blocks shared by warps
+    float *wmax;        // [2][warps] per-warp maxima of the row just written
+    int *rb_lo;         // [ncb]   first row block of a column block (band limit)
+    int *tile_start;    // [ncb+1] prefix sum of tiles per column block
+    int *first_warp;    // [ncb]
+    int *last_warp;     // [ncb]
+    int *cb_first_of;   // [warps]
+};
+
+__host__ __device__ inline size_t sweep_smem_bytes(int L) {
+    int lp = (L + 63) & ~31;
+    int ncb = (L + 31) / 32 + 1;
+    size_t f = (size_t)4 * lp + 2 * kSweepWarps * 2 * 32 + 2 * kSweepWarps;
+    size_t i = (size_t)4 * ncb + 2 + kSweepWarps;
+    return (f + i) * 4 + 64;
+}
+
+__device__ inline SweepSmem carve(unsigned char *raw, int L) {
+    SweepSmem s;
+    int lp = (L + 63) & ~31;
+    int ncb = (L + 31) / 32 + 1;
+    float *f = reinterpret_cast<float *>(raw);
+    s.row[0] = f; f += lp;
+    s.row[1] = f; f += lp;
+    s.fin_m = f; f += lp;
+    s.fin_s = f; f += lp;
+    s.part = f; f += 2 * kSweepWarps * 2 * 32;
+    s.wmax = f; f += 2 * kSweepWarps;
+    int *i = reinterpret_cast<int *>(f);
+    s.rb_lo = i; i += ncb;
+    s.tile_start = i; i += ncb + 1;
+    s.first_warp = i; i += ncb;
+    s.last_warp = i; i += ncb;
+    s.cb_first_of = i;
+    return s;
+}
+
+
+// Builds the tile plan in shared memory and returns this warp's tile range [my_lo, my_hi)
+// and the column block its range starts in.  Contains two __syncthreads().
+__device__ inline void build_tile_plan(SweepSmem &sm, int W, int K, int &my_lo, int &my_hi,
+                                       int &cb_first) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int ncb = (W + 31) >> 5;
+    if (tid == 0) {
+        int acc = 0;
+        for (int cb = 0; cb < ncb; cb++) {
+            int lo = 32 * cb + 1 - K;
+            lo = lo > 0 ? (lo >> 5) : 0;
+            sm.rb_lo[cb] = lo;
+            sm.tile_start[cb] = acc;
+            acc += cb - lo + 1;
+        }
+        sm.tile_start[ncb] = acc;
+        sm.rb_lo[ncb] = 0;
+    }
+    __syncthreads();
+    const int ntiles = sm.tile_start[ncb];
+    my_lo = (int)(((long long)warp * ntiles) / kSweepWarps);
+    my_hi = (int)(((long long)(warp + 1) * ntiles) / kSweepWarps);
+    cb_first = 0;
+    while (cb_first + 1 < ncb && sm.tile_start[cb_first + 1] <= my_lo) cb_first++;
+    if (lane == 0) sm.cb_first_of[warp] = cb_first;
+    if (tid < ncb) {
+        int a = sm.tile_start[tid], b = sm.tile_start[tid + 1] - 1;
+        int fw = 0, lw = 0;
+        for (int w = 0; w < kSweepWarps; w++) {
+            int lo = (int)(((long long)w * ntiles) / kSweepWarps);
+            int hi = (int)(((long long)(w + 1) * ntiles) / kSweepWarps);
+            if (a >= lo && a < hi) fw = w;
+            if (b >= lo && b < hi) lw = w;
+        }
+        sm.first_warp[tid] = fw;
+        sm.last_warp[tid] = lw;
+    }
+    __syncthreads();
+}
+
+}  // namespace dat

@@ -1,0 +1,349 @@
+// logsoftmax_gather forward / backward for sm_100a.
+//
+// Forward: one pass over each vocabulary row with an online (max, sum-exp) pair per
+// thread, 128-bit streaming loads, fp32 math; only the gathered values and two row
+// statistics are written.  Replaces the three-pass, scalar-load kernel of
+// fs_plugins/custom_ops/logsoftmax_gather.cu:256-310.
+// Backward: reads the logits and the row statistics and writes the dense gradient in
+// place, once, rounded once from fp32 (the reference does mul_ + scatter_add_ in the
+// logits dtype, fs_plugins/custom_ops/dag_loss.py:227-229).
+//
+// HBM-bound: algorithmic bytes are V*e per row forward and 2*V*e per row backward
+// (e = element size), plus the small index / gathered-value traffic.
+#include "dat_common.cuh"
+
+namespace dat {
+
+constexpr int kLsgThreads = 256;
+constexpr int kLsgWarps = kLsgThreads / 32;
+
+struct Strides3 {
+    int64_t b, l, s;
+};
+
+// Online update of (m, s) with `n` new values; m is the running maximum in the
+// natural domain (exact), s = sum exp(x - m).
+template <int N>
+__device__ __forceinline__ void online_update(float &m, float &s, const float (&f)[N]) {
+    float vmax = f[0];
+#pragma unroll
+    for (int i = 1; i < N; i++) vmax = fmaxf(vmax, f[i]);
+    if (vmax > m) {
+        s *= ex2((m - vmax) * kLog2e);
+        m = vmax;
+    }
+    const float mneg = -m * kLog2e;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < N; i++) acc += ex2(fmaf(f[i], kLog2e, mneg));
+    s += acc;
+}
+
+__device__ __forceinline__ void online_update1(float &m, float &s, float v) {
+    if (v > m) {
+        s *= ex2((m - v) * kLog2e);
+        m = v;
+    }
+    s += ex2((v - m) * kLog2e);
+}
+
+// Splits a row of V elements starting at `p` into a scalar head (up to the first
+// 16-byte boundary), `nvec` aligned 16-byte vectors and a scalar tail.
+template <typename T>
+__device__ __forceinline__ void row_split(const T *p, int V, int &head, int &nvec) {
+    constexpr int kVec = Elem<T>::kVec;
+    int mis = (int)((reinterpret_cast<uintptr_t>(p) & 15u) / sizeof(T));
+    head = mis ? (kVec - mis) : 0;
+    if (head > V) head = V;
+    nvec = (V - head) / kVec;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kLsgThreads)
+lsg_fwd_kernel(const T *__restrict__ x, const int64_t *__restrict__ idx, Strides3 is,
+               float *__restrict__ sel, Strides3 ss, float *__restrict__ stats,
+               int32_t *__restrict__ status, int64_t rows, int L, int S, int V) {
+    constexpr int kVec = Elem<T>::kVec;
+    __shared__ float red_m[2][kLsgWarps];
+    __shared__ float red_s[2][kLsgWarps];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int par = 0;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, par ^= 1) {
+        const T *xr = x + row * (int64_t)V;
+        int head, nvec;
+        row_split(xr, V, head, nvec);
+        const uint4 *xv = reinterpret_cast<const uint4 *>(xr + head);
+        float m = kNegBig, s = 0.f;
+        int v = tid;
+        for (; v + 3 * kLsgThreads < nvec; v += 4 * kLsgThreads) {
+            uint4 u0 = ld_stream16(xv + v);
+            uint4 u1 = ld_stream16(xv + v + kLsgThreads);
+            uint4 u2 = ld_stream16(xv + v + 2 * kLsgThreads);
+            uint4 u3 = ld_stream16(xv + v + 3 * kLsgThreads);
+            float f[4 * kVec];
+            Elem<T>::unpack(u0, f);
+            Elem<T>::unpack(u1, f + kVec);
+            Elem<T>::unpack(u2, f + 2 * kVec);
+            Elem<T>::unpack(u3, f + 3 * kVec);
+            online_update<4 * kVec>(m, s, f);
+        }
+        for (; v < nvec; v += kLsgThreads) {
+            uint4 u0 = ld_stream16(xv + v);
+            float f[kVec];
+            Elem<T>::unpack(u0, f);
+            online_update<kVec>(m, s, f);
+        }
+        // scalar head and tail
+        const int tail0 = head + nvec * kVec;
+        if (tid < head) online_update1(m, s, Elem<T>::to_float(xr[tid]));
+        if (tail0 + tid < V) online_update1(m, s, Elem<T>::to_float(xr[tail0 + tid]));
+
+        // block max (exact), then block sum of the rescaled partial sums
+        float wm = warp_max(m);
+        if (lane == 0) red_m[par][warp] = wm;
+        __syncthreads();
+        float M = red_m[par][0];
+#pragma unroll
+        for (int w = 1; w < kLsgWarps; w++) M = fmaxf(M, red_m[par][w]);
+        float sc = s * ex2((m - M) * kLog2e);
+        float ws = warp_sum(sc);
+        if (lane == 0) red_s[par][warp] = ws;
+        __syncthreads();
+        float Ssum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kLsgWarps; w++) Ssum += red_s[par][w];
+        const float logS = lg2(Ssum) * kLn2;
+
+        const int64_t b = row / L, l = row - b * L;
+        const int64_t *ir = idx + b * is.b + l * is.l;
+        float *sr = sel + b * ss.b + l * ss.l;
+        for (int k = tid; k < S; k += kLsgThreads) {
+            int64_t id = ir[(int64_t)k * is.s];
+            float val;
+            if (id >= 0 && id < V) {
+                val = (Elem<T>::to_float(xr[id]) - M) - logS;
+            } else {
+                val = __int_as_float(0x7fc00000);
+                if (status) atomicOr(status, DAT_STATUS_BAD_INDEX);
+            }
+            sr[(int64_t)k * ss.s] = val;
+        }
+        if (stats != nullptr && tid == 0) {
+            stats[2 * row] = M;
+            stats[2 * row + 1] = logS;
+        }
+    }
+}
+
+// Backward, in place.  Shared memory: S * (int + 3 float).
+template <typename T>
+__global__ void __launch_bounds__(kLsgThreads)
+lsg_bwd_kernel(T *__restrict__ x, const int64_t *__restrict__ idx, Strides3 is,
+               const float *__restrict__ g, Strides3 gs, const float *__restrict__ stats,
+               int64_t rows, int L, int S, int V) {
+    constexpr int kVec = Elem<T>::kVec;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    int *idx_s = reinterpret_cast<int *>(smem_raw);
+    float *g_s = reinterpret_cast<float *>(idx_s + S);
+    float *x_s = g_s + S;
+    float *tot_s = x_s + S;
+    __shared__ float red[kLsgWarps];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        T *xr = x + row * (int64_t)V;
+        const int64_t b = row / L, l = row - b * L;
+        const int64_t *ir = idx + b * is.b + l * is.l;
+        const float *gr = g + b * gs.b + l * gs.l;
+        __syncthreads();  // previous row's fix-ups are done with the staging arrays
+        float gsum = 0.f;
+        int nonzero = 0;
+        for (int k = tid; k < S; k += kLsgThreads) {
+            int64_t id = ir[(int64_t)k * is.s];
+            float gv = gr[(int64_t)k * gs.s];
+            bool ok = id >= 0 && id < V;
+            idx_s[k] = ok ? (int)id : -1;
+            g_s[k] = ok ? gv : 0.f;
+            x_s[k] = ok ? Elem<T>::to_float(xr[id]) : 0.f;
+            gsum += gv;
+            nonzero |= (gv != 0.f);
+        }
+        float ws = warp_sum(gsum);
+        if (lane == 0) red[warp] = ws;
+        const int any = __syncthreads_or(nonzero);
+        float G = 0.f;
+#pragma unroll
+        for (int w = 0; w < kLsgWarps; w++) G += red[w];
+
+        int head, nvec;
+        row_split(xr, V, head, nvec);
+        uint4 *xv = reinterpret_cast<uint4 *>(xr + head);
+        const int tail0 = head + nvec * kVec;
+
+        if (!any) {
+            // no gradient flows into this row (padding): the result is all zeros, no read
+            const uint4 z = make_uint4(0, 0, 0, 0);
+            for (int v = tid; v < nvec; v += kLsgThreads) xv[v] = z;
+            if (tid < head) xr[tid] = Elem<T>::from_float(0.f);
+            if (tail0 + tid < V) xr[tail0 + tid] = Elem<T>::from_float(0.f);
+            continue;
+        }
+
+        // total gradient arriving at each selected position (duplicates accumulate)
+        for (int k = tid; k < S; k += kLsgThreads) {
+            const int id = idx_s[k];
+            float t = 0.f;
+            for (int k2 = 0; k2 < S; k2++) t += (idx_s[k2] == id) ? g_s[k2] : 0.f;
+            tot_s[k] = t;
+        }
+
+        const float M = stats[2 * row], logS = stats[2 * row + 1];
+        const float c = -(M + logS) * kLog2e;
+        const float nG = -G;
+        int v = tid;
+        for (; v + kLsgThreads < nvec; v += 2 * kLsgThreads) {
+            uint4 u0 = xv[v];
+            uint4 u1 = xv[v + kLsgThreads];
+            float f[2 * kVec];
+            Elem<T>::unpack(u0, f);
+            Elem<T>::unpack(u1, f + kVec);
+#pragma unroll
+            for (int i = 0; i < 2 * kVec; i++) f[i] = nG * ex2(fmaf(f[i], kLog2e, c));
+            xv[v] = Elem<T>::pack(f);
+            xv[v + kLsgThreads] = Elem<T>::pack(f + kVec);
+        }
+        for (; v < nvec; v += kLsgThreads) {
+            uint4 u0 = xv[v];
+            float f[kVec];
+            Elem<T>::unpack(u0, f);
+#pragma unroll
+            for (int i = 0; i < kVec; i++) f[i] = nG * ex2(fmaf(f[i], kLog2e, c));
+            xv[v] = Elem<T>::pack(f);
+        }
+        if (tid < head)
+            xr[tid] = Elem<T>::from_float(nG * ex2(fmaf(Elem<T>::to_float(xr[tid]), kLog2e, c)));
+        if (tail0 + tid < V)
+            xr[tail0 + tid] = Elem<T>::from_float(
+                nG * ex2(fmaf(Elem<T>::to_float(xr[tail0 + tid]), kLog2e, c)));
+        __syncthreads();  // the whole row is written before the selected positions are fixed up
+        for (int k = tid; k < S; k += kLsgThreads) {
+            const int id = idx_s[k];
+            if (id >= 0) xr[id] = Elem<T>::from_float(fmaf(nG, ex2(fmaf(x_s[k], kLog2e, c)), tot_s[k]));
+        }
+    }
+}
+
+template <typename T>
+static int launch_fwd(const void *x, const int64_t *idx, Strides3 is, float *sel, Strides3 ss,
+                      float *stats, int32_t *status, int64_t rows, int L, int S, int V,
+                      cudaStream_t stream, const DeviceInfo &di) {
+    int per_sm = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lsg_fwd_kernel<T>, kLsgThreads, 0);
+    if (per_sm < 1) per_sm = 1;
+    int64_t grid = (int64_t)di.sm_count * per_sm;
+    if (grid > rows) grid = rows;
+    lsg_fwd_kernel<T><<<(unsigned)grid, kLsgThreads, 0, stream>>>(
+        static_cast<const T *>(x), idx, is, sel, ss, stats, status, rows, L, S, V);
+    return check_launch("dat_logsoftmax_gather");
+}
+
+template <typename T>
+static int launch_bwd(void *x, const int64_t *idx, Strides3 is, const float *g, Strides3 gs,
+                      const float *stats, int64_t rows, int L, int S, int V, cudaStream_t stream,
+                      const DeviceInfo &di) {
+    size_t smem = (size_t)S * 16;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(lsg_bwd_kernel<T>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            set_error("dat_logsoftmax_gather_backward: cannot reserve %zu bytes of shared memory", smem);
+            return DAT_ERR_UNSUPPORTED;
+        }
+    }
+    int per_sm = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lsg_bwd_kernel<T>, kLsgThreads, smem);
+    if (per_sm < 1) per_sm = 1;
+    int64_t grid = (int64_t)di.sm_count * per_sm;
+    if (grid > rows) grid = rows;
+    lsg_bwd_kernel<T><<<(unsigned)grid, kLsgThreads, smem, stream>>>(
+        static_cast<T *>(x), idx, is, g, gs, stats, rows, L, S, V);
+    return check_launch("dat_logsoftmax_gather_backward");
+}
+
+}  // namespace dat
+
+extern "C" {
+
+int dat_logsoftmax_gather(const void *word_ins_out, int dtype, const int64_t *select_idx,
+                          int64_t idx_stride_b, int64_t idx_stride_l, int64_t idx_stride_s,
+                          float *selected_result, int64_t sel_stride_b, int64_t sel_stride_l,
+                          int64_t sel_stride_s, float *row_stats, int32_t *status, int bsz,
+                          int prelen, int slen, int vocab, void *stream) {
+    using namespace dat;
+    DAT_REQUIRE(bsz >= 0 && prelen >= 0 && slen >= 0 && vocab >= 1, DAT_ERR_BAD_ARG,
+                "dat_logsoftmax_gather: bad sizes bsz=%d prelen=%d slen=%d vocab=%d", bsz, prelen,
+                slen, vocab);
+    if ((int64_t)bsz * prelen == 0) return DAT_OK;
+    DAT_REQUIRE(word_ins_out && (slen == 0 || (select_idx && selected_result)), DAT_ERR_BAD_ARG,
+                "dat_logsoftmax_gather: null pointer");
+    DeviceInfo di;
+    if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
+    const int64_t rows = (int64_t)bsz * prelen;
+    Strides3 is{idx_stride_b, idx_stride_l, idx_stride_s};
+    Strides3 ss{sel_stride_b, sel_stride_l, sel_stride_s};
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case DAT_F32:
+            return launch_fwd<float>(word_ins_out, select_idx, is, selected_result, ss, row_stats,
+                                     status, rows, prelen, slen, vocab, st, di);
+        case DAT_F16:
+            return launch_fwd<__half>(word_ins_out, select_idx, is, selected_result, ss, row_stats,
+                                      status, rows, prelen, slen, vocab, st, di);
+        case DAT_BF16:
+            return launch_fwd<__nv_bfloat16>(word_ins_out, select_idx, is, selected_result, ss,
+                                             row_stats, status, rows, prelen, slen, vocab, st, di);
+        default:
+            set_error("dat_logsoftmax_gather: unsupported dtype %d (fp32, fp16, bf16 only)", dtype);
+            return DAT_ERR_UNSUPPORTED;
+    }
+}
+
+int dat_logsoftmax_gather_backward(void *word_ins_out, int dtype, const int64_t *select_idx,
+                                   int64_t idx_stride_b, int64_t idx_stride_l,
+                                   int64_t idx_stride_s, const float *grad_selected,
+                                   int64_t g_stride_b, int64_t g_stride_l, int64_t g_stride_s,
+                                   const float *row_stats, int bsz, int prelen, int slen,
+                                   int vocab, void *stream) {
+    using namespace dat;
+    DAT_REQUIRE(bsz >= 0 && prelen >= 0 && slen >= 0 && vocab >= 1, DAT_ERR_BAD_ARG,
+                "dat_logsoftmax_gather_backward: bad sizes bsz=%d prelen=%d slen=%d vocab=%d", bsz,
+                prelen, slen, vocab);
+    if ((int64_t)bsz * prelen == 0) return DAT_OK;
+    DAT_REQUIRE(word_ins_out && row_stats && (slen == 0 || (select_idx && grad_selected)),
+                DAT_ERR_BAD_ARG, "dat_logsoftmax_gather_backward: null pointer");
+    DAT_REQUIRE(slen <= 4096, DAT_ERR_UNSUPPORTED,
+                "dat_logsoftmax_gather_backward: slen=%d exceeds 4096", slen);
+    DeviceInfo di;
+    if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
+    const int64_t rows = (int64_t)bsz * prelen;
+    Strides3 is{idx_stride_b, idx_stride_l, idx_stride_s};
+    Strides3 gs{g_stride_b, g_stride_l, g_stride_s};
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case DAT_F32:
+            return launch_bwd<float>(word_ins_out, select_idx, is, grad_selected, gs, row_stats,
+                                     rows, prelen, slen, vocab, st, di);
+        case DAT_F16:
+            return launch_bwd<__half>(word_ins_out, select_idx, is, grad_selected, gs, row_stats,
+                                      rows, prelen, slen, vocab, st, di);
+        case DAT_BF16:
+            return launch_bwd<__nv_bfloat16>(word_ins_out, select_idx, is, grad_selected, gs,
+                                             row_stats, rows, prelen, slen, vocab, st, di);
+        default:
+            set_error("dat_logsoftmax_gather_backward: unsupported dtype %d", dtype);
+            return DAT_ERR_UNSUPPORTED;
+    }
+}
+
+}  // extern "C"

@@ -1,0 +1,50 @@
+"""Data-parallel glue of the hot path: one process per GPU, the batch of sentences is
+sharded by rank and the only exchange is one SUM all-reduce of a few scalars.
+
+The ops have no parameters and every sentence is independent, so no tensor ever crosses
+GPUs; what the reference all-reduces after the loss is its logging buffer
+(fairseq/trainer.py:1453-1491 -> fairseq/distributed/utils.py:634-680, one fp64 buffer).
+``all_reduce_stats`` reproduces that collective for the quantities this path produces.
+It works with any ``torch.distributed`` backend (NCCL on GPUs, gloo on CPU for tests).
+"""
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(n: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous [start, end) slice of ``n`` sentences owned by ``rank``."""
+    per = (n + world - 1) // world
+    return min(n, rank * per), min(n, (rank + 1) * per)
+
+
+def sentence_stats(loss_result: torch.Tensor, target_length: torch.Tensor) -> torch.Tensor:
+    """Per-shard statistics as an fp64 vector
+    ``[sum_b loss_b / tl_b, sum_b tl_b, n_sentences, n_invalid]``.
+
+    Mirrors fs_plugins/criterions/nat_dag_loss.py:190-194: sentences whose
+    log-likelihood is inf/nan are zeroed and counted as invalid.  No host sync."""
+    invalid = loss_result.isinf().logical_or(loss_result.isnan())
+    clean = loss_result.masked_fill(invalid, 0).to(torch.float64)
+    tl = target_length.to(torch.float64)
+    return torch.stack([
+        (clean / tl).sum(),
+        tl.sum(),
+        torch.tensor(float(loss_result.numel()), dtype=torch.float64, device=loss_result.device),
+        invalid.sum().to(torch.float64),
+    ])
+
+
+def all_reduce_stats(stats: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """SUM all-reduce of the statistics vector, enqueued on the current stream (no host
+    sync).  A no-op when torch.distributed is not initialised."""
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.SUM, group=group)
+    return stats
+
+
+def global_loss(stats: torch.Tensor) -> torch.Tensor:
+    """The criterion's scalar ``-(loss / target_length).mean()`` over the GLOBAL batch,
+    from the reduced statistics."""
+    return -(stats[0] / stats[2])

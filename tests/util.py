@@ -30,3 +30,28 @@ def assert_rel(actual, ref, tol, what=""):
     e = rel_err(actual, ref)
     assert e <= tol, f"{what}: max|d|/max|ref| = {e:.3e} > {tol:.1e}"
     return e
+
+
+_PRECISION_BITS = {"float16": 11, "bfloat16": 8}
+
+
+def assert_rel_quantized(actual, ref, tol, dtype_name, what=""):
+    """Like assert_rel for a result that was rounded ONCE to a 16-bit format: the part of
+    each element's error that exceeds the format's own half-ulp must stay within
+    tol * max|ref|.  (bf16 keeps 8 significant bits, so correct rounding alone is off by up
+    to 2^-9..2^-8 of an element, more than the 2e-3 budget; fp16 keeps 11 bits.)"""
+    actual = np.asarray(actual, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    assert actual.shape == ref.shape
+    assert np.isfinite(actual).all() and np.isfinite(ref).all()
+    bits = _PRECISION_BITS[dtype_name]
+    mag = np.abs(ref)
+    expo = np.floor(np.log2(np.where(mag > 0, mag, 1.0)))
+    half_ulp = np.where(mag > 0, 2.0 ** (expo - bits), 0.0)
+    if dtype_name == "float16":
+        half_ulp = np.maximum(half_ulp, 2.0 ** -25)   # subnormal spacing
+    excess = np.maximum(np.abs(actual - ref) - half_ulp, 0.0)
+    scale = mag.max() if mag.max() > 0 else 1.0
+    e = float(excess.max() / scale)
+    assert e <= tol, f"{what}: error beyond the {dtype_name} half-ulp = {e:.3e} * max|ref| > {tol:.1e}"
+    return e
