@@ -53,7 +53,7 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
     const int W = ol - tl + 1;
     const float *match = match_all + (size_t)b * T * L;
     const float *band = links + (size_t)b * L * K;
-    SweepSmem sm = carve(smem_raw, L);
+    const SweepSmem sm = carve(smem_raw, L);
     // the partial-merge slots hold (value, rank) pairs here
     int *part_r = reinterpret_cast<int *>(sm.part);
     int *fin_r = reinterpret_cast<int *>(sm.fin_s);
@@ -63,7 +63,8 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
                           : trace_ws + (size_t)b * T * L;
     const int tstride = kTraceInSmem ? W : L;
 
-    for (int x = tid; x < L + 32; x += kSweepThreads) sm.row[0][x] = -INFINITY;
+    const int pitch = sweep_row_pitch(L);
+    for (int x = tid; x < 2 * pitch; x += kSweepThreads) sm.row0[x] = -INFINITY;  // row0 and row1
     int my_lo, my_hi, cb_first;
     build_tile_plan(sm, W, K, my_lo, my_hi, cb_first);
     // warps without tiles sit between the first and last warp of a shared column block:
@@ -74,17 +75,18 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
         sm.part[o + lane] = -INFINITY;
         part_r[o + 32 + lane] = kRankNone;
     }
-    if (tid == 0) sm.row[0][0] = match[0];
+    if (tid == 0) sm.row0[0] = match[0];
     __syncthreads();
 
+    const unsigned stride = (unsigned)(K - 1);
     for (int t = 1; t < tl; t++) {
-        const float *prev = sm.row[(t - 1) & 1];
-        float *cur = sm.row[t & 1];
+        const float *prev = (t & 1) ? sm.row0 : sm.row1;  // row of step t-1, window coordinates
+        float *cur = (t & 1) ? sm.row1 : sm.row0;
         float mt[2];
 #pragma unroll
         for (int q = 0; q < 2; q++) {
             int c = tid + q * kSweepThreads;
-            mt[q] = (c < W) ? match[(size_t)t * L + t + c] : 0.f;
+            mt[q] = (c < W) ? __ldg(match + (size_t)t * L + t + c) : 0.f;
         }
         if (my_lo < my_hi) {
             int cb = cb_first;
@@ -92,29 +94,46 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
             bool owns_start = (my_lo == sm.tile_start[cb]);
             float bv = -INFINITY;
             int br = kRankNone;
+            const unsigned row_base = (unsigned)(t - 1) * (unsigned)K;
             for (int tile = my_lo; tile < my_hi;) {
-                const int c = 32 * cb + lane;
-                int rmax = (c < W) ? c : -1;
-                int rmin = c + 1 - K; rmin = rmin > 0 ? rmin : 0;
-                const int r0 = 32 * rb;
-                int r1 = r0 + 32;
-                { int cap = 32 * cb + 32; cap = cap < W ? cap : W; if (r1 > cap) r1 = cap; }
-                const float *bp = band + (size_t)(t - 1) * K + c;
-                const int i0 = t - 1;
-                for (int r = r0; r < r1; r += kChunk) {
-                    float x[kChunk];
+                const TileGeom g = tile_geom(cb, rb, lane, W, K);
+                const unsigned off0 = row_base + (unsigned)g.c;
+                if (g.interior) {
+#pragma unroll 1
+                    for (int r = g.r0; r < g.r0 + 32; r += kChunk) {
+                        const float4 p0 = *reinterpret_cast<const float4 *>(prev + r);
+                        const float4 p1 = *reinterpret_cast<const float4 *>(prev + r + 4);
+                        const float pa[kChunk] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+                        const unsigned o = off0 + (unsigned)r * stride;
+                        float x[kChunk];
 #pragma unroll
-                    for (int u = 0; u < kChunk; u++) {
-                        const int rr = r + u;
-                        const bool ok = (rr >= rmin) && (rr <= rmax) && (rr < r1);
-                        float lk = ok ? __ldg(bp + (size_t)rr * (K - 1)) : -INFINITY;
-                        float pa = prev[i0 + (rr < r1 ? rr : r1 - 1)];
-                        x[u] = __fadd_rn(pa, lk);
+                        for (int u = 0; u < kChunk; u++) x[u] = __ldg(band + (o + (unsigned)u * stride));
+#pragma unroll
+                        for (int u = 0; u < kChunk; u++) x[u] = __fadd_rn(pa[u], x[u]);
+                        float cm = x[0];
+#pragma unroll
+                        for (int u = 1; u < kChunk; u++) cm = fmaxf(cm, x[u]);
+                        if (cm >= bv && cm > -INFINITY) {  // some candidate of the chunk may win or tie
+#pragma unroll
+                            for (int u = 0; u < kChunk; u++)
+                                if (x[u] >= bv) better(bv, br, x[u], tie_rank(g.c - (r + u) + 1, lg));
+                        }
                     }
+                } else {
+#pragma unroll 1
+                    for (int r = g.r0; r < g.r1; r += kChunk) {
+                        float x[kChunk];
 #pragma unroll
-                    for (int u = 0; u < kChunk; u++) {
-                        const int d = c - (r + u) + 1;  // j - i
-                        if (x[u] >= bv && x[u] > -INFINITY) better(bv, br, x[u], tie_rank(d, lg));
+                        for (int u = 0; u < kChunk; u++) {
+                            const int rr = r + u;
+                            const bool ok = (rr >= g.rmin) && (rr <= g.rmax);
+                            const float lk = ok ? __ldg(band + (off0 + (unsigned)rr * stride)) : -INFINITY;
+                            x[u] = __fadd_rn(prev[rr], lk);  // rows past the window read the -inf padding
+                        }
+#pragma unroll
+                        for (int u = 0; u < kChunk; u++)
+                            if (x[u] >= bv && x[u] > -INFINITY)
+                                better(bv, br, x[u], tie_rank(g.c - (r + u) + 1, lg));
                     }
                 }
                 tile++;
@@ -122,7 +141,7 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
                 if (rb > cb || tile == my_hi) {
                     const bool complete = owns_start && (rb > cb);
                     if (complete) {
-                        if (c < W) { sm.fin_m[c] = bv; fin_r[c] = br; }
+                        if (g.c < W) { sm.fin_m[g.c] = bv; fin_r[g.c] = br; }
                     } else {
                         const int which = (cb == cb_first) ? 0 : 1;
                         const int o = ((which * kSweepWarps + warp) * 2) * 32;
@@ -158,10 +177,11 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
                         better(bv, br, sm.part[o + ln], part_r[o + 32 + ln]);
                     }
                 }
-                const int j = t + c;
-                cur[j] = __fadd_rn(bv, mt[q]);
+                float v = __fadd_rn(bv, mt[q]);
+                if (!(v > -INFINITY)) v = -INFINITY;  // keeps the -inf padding convention under NaN
+                cur[c] = v;
                 const int d = (br == kRankNone) ? 0 : (br & 0xfffff);
-                trace[(size_t)t * tstride + (kTraceInSmem ? c : j)] = (uint16_t)d;
+                trace[(size_t)t * tstride + (kTraceInSmem ? c : (t + c))] = (uint16_t)d;
             }
         }
         __syncthreads();
@@ -169,7 +189,7 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
 
     // backtrace (dag_best_alignment.cu:185-188), one thread
     if (tid == 0) {
-        const float score = sm.row[(tl - 1) & 1][ol - 1];
+        const float score = (((tl - 1) & 1) ? sm.row1 : sm.row0)[W - 1];
         if (max_score) max_score[b] = score;
         if (score > -INFINITY) {
             int pos = ol - 1;

@@ -16,9 +16,28 @@
 //
 // Layout of `offsets` per sentence (2*T+2 doubles): [0,T) alpha row offsets, [T,2T) beta
 // row offsets, [2T] log2-likelihood from the alpha sweep, [2T+1] from the beta sweep.
+//
+// The band of one sentence (<= 4 MB) is re-read at every target step and is served by
+// L2; per term the inner loops issue one coalesced 4-byte load, a quarter of a 128-bit
+// shared-memory broadcast, one FFMA, one FMNMX, two FADD and one MUFU.EX2.
 #include "dag_tiles.cuh"
 
 namespace dat {
+
+// One chunk of kChunk rows for 32 columns: online log-sum-exp update of (m, s).
+__device__ __forceinline__ void lse_chunk(float &m, float &s, const float (&x)[kChunk]) {
+    float cm = x[0];
+#pragma unroll
+    for (int u = 1; u < kChunk; u++) cm = fmaxf(cm, x[u]);
+    if (cm > m) {
+        s *= ex2(m - cm);
+        m = cm;
+    }
+    float acc = 0.f;
+#pragma unroll
+    for (int u = 0; u < kChunk; u++) acc += ex2(x[u] - m);
+    s += acc;
+}
 
 // ---------------------------------------------------------------------------------
 // alpha sweep
@@ -28,12 +47,12 @@ __device__ void alpha_sweep(const float *__restrict__ match, const float *__rest
                             int ol, int tl, int T, int L, int K, unsigned char *raw) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int W = ol - tl + 1;
-    const int ncb = (W + 31) >> 5;
-    SweepSmem sm = carve(raw, L);
+    const SweepSmem sm = carve(raw, L);
+    const int pitch = sweep_row_pitch(L);
     __shared__ double off_s;
     __shared__ float delta_s;
 
-    for (int x = tid; x < L + 32; x += kSweepThreads) sm.row[0][x] = -INFINITY;
+    for (int x = tid; x < 2 * pitch; x += kSweepThreads) sm.row0[x] = -INFINITY;  // row0 and row1
     int my_lo, my_hi, cb_first;
     build_tile_plan(sm, W, K, my_lo, my_hi, cb_first);
     // warps without tiles sit between the first and last warp of a shared column block:
@@ -46,7 +65,7 @@ __device__ void alpha_sweep(const float *__restrict__ match, const float *__rest
     }
     const float m00 = match[0] * kLog2e;
     if (tid == 0) {
-        sm.row[0][0] = m00;
+        sm.row0[0] = m00;
         alpha[0] = m00;
         offs[0] = 0.0;
         off_s = 0.0;
@@ -56,19 +75,21 @@ __device__ void alpha_sweep(const float *__restrict__ match, const float *__rest
     for (int c = 1 + tid; c < W; c += kSweepThreads) alpha[c] = -INFINITY;
     __syncthreads();
 
+    const unsigned stride = (unsigned)(K - 1);
     for (int t = 1; t < tl; t++) {
-        const float *prev = sm.row[(t - 1) & 1];
-        float *cur = sm.row[t & 1];
+        const float *prev = (t & 1) ? sm.row0 : sm.row1;  // row of step t-1
+        float *cur = (t & 1) ? sm.row1 : sm.row0;
         // match of this thread's merge columns, requested early
         float mt[2];
 #pragma unroll
         for (int q = 0; q < 2; q++) {
             int c = tid + q * kSweepThreads;
-            mt[q] = (c < W) ? match[(size_t)t * L + t + c] : 0.f;
+            mt[q] = (c < W) ? __ldg(match + (size_t)t * L + t + c) : 0.f;
         }
         if (tid == 0) {
-            float d = sm.wmax[((t - 1) & 1) * kSweepWarps];
-            for (int w = 1; w < kSweepWarps; w++) d = fmaxf(d, sm.wmax[((t - 1) & 1) * kSweepWarps + w]);
+            const float *wm = sm.wmax + ((t - 1) & 1) * kSweepWarps;
+            float d = wm[0];
+            for (int w = 1; w < kSweepWarps; w++) d = fmaxf(d, wm[w]);
             if (!(d > 0.5f * kNegBig)) d = 0.f;  // dead row
             delta_s = d;
             off_s += (double)d;
@@ -81,43 +102,45 @@ __device__ void alpha_sweep(const float *__restrict__ match, const float *__rest
             int rb = sm.rb_lo[cb] + (my_lo - sm.tile_start[cb]);
             bool owns_start = (my_lo == sm.tile_start[cb]);
             float m = kNegBig, s = 0.f;
+            const unsigned row_base = (unsigned)(t - 1) * (unsigned)K;
             for (int tile = my_lo; tile < my_hi;) {
-                const int c = 32 * cb + lane;
-                int rmax = (c < W) ? c : -1;               // valid rows of this lane: [rmin, rmax]
-                int rmin = c + 1 - K; rmin = rmin > 0 ? rmin : 0;
-                const int r0 = 32 * rb;
-                int r1 = r0 + 32;
-                { int cap = 32 * cb + 32; cap = cap < W ? cap : W; if (r1 > cap) r1 = cap; }
-                const float *bp = band + (size_t)(t - 1) * K + c;
-                const int i0 = t - 1;
-                for (int r = r0; r < r1; r += kChunk) {
-                    float x[kChunk];
+                const TileGeom g = tile_geom(cb, rb, lane, W, K);
+                // element (r, c) sits at band[(t-1+r)*K + (c-r)] = band[row_base + c + r*(K-1)]
+                const unsigned off0 = row_base + (unsigned)g.c;
+                if (g.interior) {
+#pragma unroll 1
+                    for (int r = g.r0; r < g.r0 + 32; r += kChunk) {
+                        const float4 p0 = *reinterpret_cast<const float4 *>(prev + r);
+                        const float4 p1 = *reinterpret_cast<const float4 *>(prev + r + 4);
+                        const float pa[kChunk] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+                        const unsigned o = off0 + (unsigned)r * stride;
+                        float x[kChunk];
 #pragma unroll
-                    for (int u = 0; u < kChunk; u++) {
-                        const int rr = r + u;
-                        const bool ok = (rr >= rmin) && (rr <= rmax) && (rr < r1);
-                        float lk = ok ? __ldg(bp + (size_t)rr * (K - 1)) : -INFINITY;
-                        float pa = prev[i0 + (rr < r1 ? rr : r1 - 1)];
-                        x[u] = fmaf(lk, kLog2e, pa);
+                        for (int u = 0; u < kChunk; u++) x[u] = __ldg(band + (o + (unsigned)u * stride));
+#pragma unroll
+                        for (int u = 0; u < kChunk; u++) x[u] = fmaf(x[u], kLog2e, pa[u]);
+                        lse_chunk(m, s, x);
                     }
-                    float cm = x[0];
+                } else {
+#pragma unroll 1
+                    for (int r = g.r0; r < g.r1; r += kChunk) {
+                        float x[kChunk];
 #pragma unroll
-                    for (int u = 1; u < kChunk; u++) cm = fmaxf(cm, x[u]);
-                    if (cm > m) {
-                        s *= ex2(m - cm);
-                        m = cm;
+                        for (int u = 0; u < kChunk; u++) {
+                            const int rr = r + u;
+                            const bool ok = (rr >= g.rmin) && (rr <= g.rmax);
+                            const float lk = ok ? __ldg(band + (off0 + (unsigned)rr * stride)) : -INFINITY;
+                            x[u] = fmaf(lk, kLog2e, prev[rr]);  // rows past the window read the -inf padding
+                        }
+                        lse_chunk(m, s, x);
                     }
-                    float acc = 0.f;
-#pragma unroll
-                    for (int u = 0; u < kChunk; u++) acc += ex2(x[u] - m);
-                    s += acc;
                 }
                 tile++;
                 rb++;
                 if (rb > cb || tile == my_hi) {
                     const bool complete = owns_start && (rb > cb);
                     if (complete) {
-                        if (c < W) { sm.fin_m[c] = m; sm.fin_s[c] = s; }
+                        if (g.c < W) { sm.fin_m[g.c] = m; sm.fin_s[g.c] = s; }
                     } else {
                         const int which = (cb == cb_first) ? 0 : 1;
                         float *p = sm.part + ((which * kSweepWarps + warp) * 2) * 32;
@@ -159,9 +182,8 @@ __device__ void alpha_sweep(const float *__restrict__ match, const float *__rest
                 float u = -INFINITY;
                 if (s > 0.f) u = (m + lg2(s) - delta) + mt[q] * kLog2e;
                 if (!(u > -INFINITY)) u = -INFINITY;  // also catches a NaN from +inf match
-                const int j = t + c;
-                cur[j] = u;
-                alpha[(size_t)t * L + j] = u;
+                cur[c] = u;
+                alpha[(size_t)t * L + t + c] = u;
                 vmax = fmaxf(vmax, u);
             }
         }
@@ -170,7 +192,8 @@ __device__ void alpha_sweep(const float *__restrict__ match, const float *__rest
         __syncthreads();
     }
     if (tid == 0) {
-        float u = sm.row[(tl - 1) & 1][ol - 1];
+        const float *last = ((tl - 1) & 1) ? sm.row1 : sm.row0;
+        float u = last[W - 1];
         double z2 = (u > -INFINITY) ? (double)u + off_s : -INFINITY;
         offs[2 * T] = z2;
         if (loss_out) *loss_out = (float)(z2 * kLn2d);
@@ -178,36 +201,53 @@ __device__ void alpha_sweep(const float *__restrict__ match, const float *__rest
 }
 
 // ---------------------------------------------------------------------------------
-// beta sweep: one warp per pair of window rows (r, W-1-r), lanes along the band row
+// beta sweep: one warp per window row, lanes along the band row (coalesced), per-lane
+// online accumulators reduced once per row
 // ---------------------------------------------------------------------------------
-__device__ __forceinline__ void beta_row(const float *__restrict__ brow, const float *next_j,
-                                         int len, int lane, float &m, float &s) {
-    // log-sum-exp over e in [0,len) of next_j[e] + brow[e] * log2(e)
+template <int NS, bool kMasked>
+__device__ __forceinline__ void beta_chunk(const float *__restrict__ brow, const float *next_c, int e0,
+                                           int len, int lane, float &m, float &s) {
+    float x[NS];
+#pragma unroll
+    for (int u = 0; u < NS; u++) {
+        const int e = e0 + u * 32 + lane;
+        if (kMasked) {
+            const bool ok = e < len;
+            const float lk = ok ? __ldg(brow + e) : -INFINITY;
+            x[u] = fmaf(lk, kLog2e, next_c[ok ? e : 0]);
+        } else {
+            x[u] = fmaf(__ldg(brow + e), kLog2e, next_c[e]);
+        }
+    }
+    float cm = x[0];
+#pragma unroll
+    for (int u = 1; u < NS; u++) cm = fmaxf(cm, x[u]);
+    if (cm > m) {
+        s *= ex2(m - cm);
+        m = cm;
+    }
+    float acc = 0.f;
+#pragma unroll
+    for (int u = 0; u < NS; u++) acc += ex2(x[u] - m);
+    s += acc;
+}
+
+// log2-sum-exp2 over e in [0,len) of next_c[e] + brow[e]*log2(e); returns (m, s) reduced
+// over the warp.
+__device__ __forceinline__ void beta_row(const float *__restrict__ brow, const float *next_c, int len,
+                                         int lane, float &m, float &s) {
     m = kNegBig;
     s = 0.f;
-    for (int e0 = 0; e0 < len; e0 += 32 * kChunk) {
-        float x[kChunk];
-#pragma unroll
-        for (int u = 0; u < kChunk; u++) {
-            const int e = e0 + u * 32 + lane;
-            const bool ok = e < len;
-            float lk = ok ? __ldg(brow + e) : -INFINITY;
-            float nb = next_j[ok ? e : 0];
-            x[u] = fmaf(lk, kLog2e, nb);
-        }
-        float cm = x[0];
-#pragma unroll
-        for (int u = 1; u < kChunk; u++) cm = fmaxf(cm, x[u]);
-        if (cm > m) {
-            s *= ex2(m - cm);
-            m = cm;
-        }
-        float acc = 0.f;
-#pragma unroll
-        for (int u = 0; u < kChunk; u++) acc += ex2(x[u] - m);
-        s += acc;
-    }
-    warp_lse(m, s);
+    int e0 = 0;
+    for (; e0 + 256 <= len; e0 += 256) beta_chunk<8, false>(brow, next_c, e0, len, lane, m, s);
+    const int rem = len - e0;
+    if (rem > 128) beta_chunk<8, true>(brow, next_c, e0, len, lane, m, s);
+    else if (rem > 64) beta_chunk<4, true>(brow, next_c, e0, len, lane, m, s);
+    else if (rem > 32) beta_chunk<2, true>(brow, next_c, e0, len, lane, m, s);
+    else if (rem > 0) beta_chunk<1, true>(brow, next_c, e0, len, lane, m, s);
+    const float M = warp_max(m);
+    s = warp_sum(s * ex2(m - M));
+    m = M;
 }
 
 __device__ void beta_sweep(const float *__restrict__ match, const float *__restrict__ band,
@@ -215,18 +255,17 @@ __device__ void beta_sweep(const float *__restrict__ match, const float *__restr
                            int ol, int tl, int T, int L, int K, unsigned char *raw) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int W = ol - tl + 1;
-    SweepSmem sm = carve(raw, L);
+    const SweepSmem sm = carve(raw, L);
+    const int pitch = sweep_row_pitch(L);
     double *offb = offs + T;
 
-    for (int x = tid; x < L + 32; x += kSweepThreads) {
-        sm.row[0][x] = -INFINITY;
-        sm.row[1][x] = -INFINITY;
-    }
+    for (int x = tid; x < 2 * pitch; x += kSweepThreads) sm.row0[x] = -INFINITY;
     __syncthreads();
     float mll = match[(size_t)(tl - 1) * L + (ol - 1)] * kLog2e;
     if (!(mll > -INFINITY)) mll = -INFINITY;
     if (tid == 0) {
-        sm.row[(tl - 1) & 1][ol - 1] = mll;
+        float *last = ((tl - 1) & 1) ? sm.row1 : sm.row0;
+        last[W - 1] = mll;
         beta[(size_t)(tl - 1) * L + (ol - 1)] = mll;
         offb[tl - 1] = 0.0;
         for (int w = 0; w < kSweepWarps; w++) sm.wmax[((tl - 1) & 1) * kSweepWarps + w] = mll;
@@ -236,10 +275,9 @@ __device__ void beta_sweep(const float *__restrict__ match, const float *__restr
     double off = 0.0;  // thread 0 only
     __syncthreads();
 
-    const int npairs = (W + 1) >> 1;
     for (int t = tl - 2; t >= 0; t--) {
-        const float *next = sm.row[(t + 1) & 1];
-        float *cur = sm.row[t & 1];
+        const float *next = ((t + 1) & 1) ? sm.row1 : sm.row0;
+        float *cur = (t & 1) ? sm.row1 : sm.row0;
         float delta;
         {
             float d = (lane < kSweepWarps) ? sm.wmax[((t + 1) & 1) * kSweepWarps + lane] : kNegBig;
@@ -252,32 +290,31 @@ __device__ void beta_sweep(const float *__restrict__ match, const float *__restr
             offb[t] = off;
         }
         float vmax = kNegBig;
-        for (int p = warp; p < npairs; p += kSweepWarps) {
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const int r = h == 0 ? p : (W - 1 - p);
-                if (h == 1 && r == p) break;
-                const int i = t + r;
-                int len = W - r;
-                len = len < K ? len : K;
-                const float mt = (lane == 0) ? match[(size_t)t * L + i] : 0.f;
-                float m, s;
-                beta_row(band + (size_t)i * K, next + t + 1 + r, len, lane, m, s);
-                if (lane == 0) {
-                    float u = -INFINITY;
-                    if (s > 0.f) u = (m + lg2(s) - delta) + mt * kLog2e;
-                    if (!(u > -INFINITY)) u = -INFINITY;
-                    cur[i] = u;
-                    beta[(size_t)t * L + i] = u;
-                    vmax = fmaxf(vmax, u);
-                }
+        // rows are dealt in snake order (w, 31-w, 32+w, 63-w, ...) so that every warp gets
+        // the same mix of long and short rows
+        for (int p = 0; p < ((W + 31) >> 5) * 2; p++) {
+            const int r = (p >> 1) * 32 + ((p & 1) ? (31 - warp) : warp);
+            if (r >= W) continue;
+            const int i = t + r;
+            int len = W - r;
+            len = len < K ? len : K;
+            const float mt = (lane == 0) ? __ldg(match + (size_t)t * L + i) : 0.f;
+            float m, s;
+            beta_row(band + (size_t)i * K, next + r, len, lane, m, s);
+            if (lane == 0) {
+                float u = -INFINITY;
+                if (s > 0.f) u = (m + lg2(s) - delta) + mt * kLog2e;
+                if (!(u > -INFINITY)) u = -INFINITY;
+                cur[r] = u;
+                beta[(size_t)t * L + i] = u;
+                vmax = fmaxf(vmax, u);
             }
         }
         if (lane == 0) sm.wmax[(t & 1) * kSweepWarps + warp] = vmax;
         __syncthreads();
     }
     if (tid == 0) {
-        float u = sm.row[0][0];
+        float u = sm.row0[0];
         double z2 = (u > -INFINITY) ? (double)u + off : -INFINITY;
         offs[2 * T + 1] = z2;
         if (loss_out) *loss_out = (float)(z2 * kLn2d);
@@ -339,6 +376,8 @@ int dat_dag_loss(const float *match_all, const float *links, const int64_t *outp
                 "dat_dag_loss: beta workspace required when require_gradient");
     DAT_REQUIRE(prelen <= 2 * kSweepThreads, DAT_ERR_UNSUPPORTED,
                 "dat_dag_loss: prelen=%d exceeds %d", prelen, 2 * kSweepThreads);
+    DAT_REQUIRE((long long)prelen * translen < (1ll << 31), DAT_ERR_UNSUPPORTED,
+                "dat_dag_loss: prelen*translen too large");
     DeviceInfo di;
     if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
     const size_t smem = sweep_smem_bytes(prelen);

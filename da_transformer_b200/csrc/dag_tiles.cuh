@@ -6,6 +6,10 @@
 // contiguous ranges of (almost) equal length, one per warp.  A warp keeps one accumulator
 // per lane (= column) while it walks the tiles of a column block; a column block shared by
 // several warps is merged through shared memory.
+//
+// Recursion rows live in shared memory in WINDOW coordinates (entry r of the row of step t
+// is vertex t + r), so the 4 / 8 consecutive rows a chunk needs are one or two aligned
+// 128-bit broadcast loads.
 #pragma once
 
 #include "dat_common.cuh"
@@ -20,21 +24,25 @@ __host__ __device__ inline bool lengths_valid(long long ol, long long tl, int T,
     return tl >= 2 && ol >= 2 && ol >= tl && ol <= L && tl <= T;
 }
 
+// Shared-memory carve-up (plain pointers: a struct indexed at run time would live in
+// local memory).
 struct SweepSmem {
-    float *row[2];      // recursion rows, indexed by absolute vertex
-    float *fin_m;       // per window column: merged running max / sum
+    float *row0, *row1;  // recursion rows, window coordinates, padded with -inf
+    float *fin_m;        // per window column: merged running max / sum
     float *fin_s;
-    float *part;        // [2][warps][2][32] partial (m, s) of column blocks shared by warps
-    float *wmax;        // [2][warps] per-warp maxima of the row just written
-    int *rb_lo;         // [ncb]   first row block of a column block (band limit)
-    int *tile_start;    // [ncb+1] prefix sum of tiles per column block
-    int *first_warp;    // [ncb]
-    int *last_warp;     // [ncb]
-    int *cb_first_of;   // [warps]
+    float *part;         // [2][warps][2][32] partial (m, s) of column blocks shared by warps
+    float *wmax;         // [2][warps] per-warp maxima of the row just written
+    int *rb_lo;          // [ncb+1] first row block of a column block (band limit)
+    int *tile_start;     // [ncb+1] prefix sum of tiles per column block
+    int *first_warp;     // [ncb]
+    int *last_warp;      // [ncb]
+    int *cb_first_of;    // [warps]
 };
 
+__host__ __device__ inline int sweep_row_pitch(int L) { return (L + 63) & ~31; }
+
 __host__ __device__ inline size_t sweep_smem_bytes(int L) {
-    int lp = (L + 63) & ~31;
+    int lp = sweep_row_pitch(L);
     int ncb = (L + 31) / 32 + 1;
     size_t f = (size_t)4 * lp + 2 * kSweepWarps * 2 * 32 + 2 * kSweepWarps;
     size_t i = (size_t)4 * ncb + 2 + kSweepWarps;
@@ -43,11 +51,11 @@ __host__ __device__ inline size_t sweep_smem_bytes(int L) {
 
 __device__ inline SweepSmem carve(unsigned char *raw, int L) {
     SweepSmem s;
-    int lp = (L + 63) & ~31;
+    int lp = sweep_row_pitch(L);
     int ncb = (L + 31) / 32 + 1;
     float *f = reinterpret_cast<float *>(raw);
-    s.row[0] = f; f += lp;
-    s.row[1] = f; f += lp;
+    s.row0 = f; f += lp;
+    s.row1 = f; f += lp;
     s.fin_m = f; f += lp;
     s.fin_s = f; f += lp;
     s.part = f; f += 2 * kSweepWarps * 2 * 32;
@@ -61,10 +69,9 @@ __device__ inline SweepSmem carve(unsigned char *raw, int L) {
     return s;
 }
 
-
 // Builds the tile plan in shared memory and returns this warp's tile range [my_lo, my_hi)
 // and the column block its range starts in.  Contains two __syncthreads().
-__device__ inline void build_tile_plan(SweepSmem &sm, int W, int K, int &my_lo, int &my_hi,
+__device__ inline void build_tile_plan(const SweepSmem &sm, int W, int K, int &my_lo, int &my_hi,
                                        int &cb_first) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int ncb = (W + 31) >> 5;
@@ -100,6 +107,30 @@ __device__ inline void build_tile_plan(SweepSmem &sm, int W, int K, int &my_lo, 
         sm.last_warp[tid] = lw;
     }
     __syncthreads();
+}
+
+// Geometry of one tile for one lane.
+struct TileGeom {
+    int c;        // window column of this lane
+    int r0, r1;   // row range of the tile (r1 exclusive, clipped to the triangle)
+    int rmin, rmax;  // valid rows of this lane (band limit, diagonal); rmax < rmin if none
+    bool interior;   // every (row, lane) pair of the tile is a valid, in-bounds term
+};
+
+__device__ __forceinline__ TileGeom tile_geom(int cb, int rb, int lane, int W, int K) {
+    TileGeom g;
+    g.c = 32 * cb + lane;
+    g.rmax = (g.c < W) ? g.c : -1;
+    int rmin = g.c + 1 - K;
+    g.rmin = rmin > 0 ? rmin : 0;
+    g.r0 = 32 * rb;
+    int cap = 32 * cb + 32;
+    cap = cap < W ? cap : W;
+    g.r1 = (g.r0 + 32 < cap) ? g.r0 + 32 : cap;
+    // strictly below the diagonal block, the whole 32x32 square inside the band, and the
+    // lanes past W (last column block) still address valid memory: c - r < K
+    g.interior = (rb < cb) && (32 * cb + 31 - g.r0 < K);
+    return g;
 }
 
 }  // namespace dat

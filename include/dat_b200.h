@@ -141,6 +141,14 @@ int dat_dag_best_alignment(const float *match_all, const float *links,
                            int bsz, int tarlen, int prelen, int translen, int config,
                            void *stream);
 
+/*
+ * Measurement helper, no counterpart in the reference: launches `blocks` CTAs of 1024
+ * threads that each execute 8*iters dependent-chain ex2 evaluations per thread, so that
+ * blocks*1024*8*iters / elapsed is the device's sustained special-function rate (the
+ * roofline denominator of the DAG recursion kernels).  `sink` is one device float.
+ */
+int dat_probe_mufu(int iters, int blocks, float *sink, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
