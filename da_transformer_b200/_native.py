@@ -20,7 +20,7 @@ EXPORTS = (
     "dat_version", "dat_last_error", "dat_status_string", "dat_dag_loss_offsets_bytes",
     "dat_dag_best_alignment_workspace_bytes", "dat_logsoftmax_gather",
     "dat_logsoftmax_gather_backward", "dat_dag_loss", "dat_dag_loss_backward",
-    "dat_dag_best_alignment", "dat_probe_mufu",
+    "dat_dag_best_alignment", "dat_probe_mufu", "dat_dag_loss_static",
 )
 
 _lib = None
@@ -49,6 +49,8 @@ def _declare(lib):
     lib.dat_dag_loss_backward.argtypes = [_vp] * 10 + [_i32] * 6 + [_vp]
     lib.dat_dag_best_alignment.restype = _i32
     lib.dat_dag_best_alignment.argtypes = [_vp] * 8 + [_i32] * 5 + [_vp]
+    lib.dat_dag_loss_static.restype = _i32
+    lib.dat_dag_loss_static.argtypes = [_vp] * 6 + [_i32] * 4 + [_vp]
     lib.dat_probe_mufu.restype = _i32
     lib.dat_probe_mufu.argtypes = [_i32, _i32, _vp, _vp]
 

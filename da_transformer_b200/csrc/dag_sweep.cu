@@ -20,6 +20,8 @@
 // The band of one sentence (<= 4 MB) is re-read at every target step and is served by
 // L2; per term the inner loops issue one coalesced 4-byte load, a quarter of a 128-bit
 // shared-memory broadcast, one FFMA, one FMNMX, two FADD and one MUFU.EX2.
+#include <mutex>
+
 #include "dag_tiles.cuh"
 
 namespace dat {
@@ -397,3 +399,97 @@ int dat_dag_loss(const float *match_all, const float *links, const int64_t *outp
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// Likelihood without any allocation by anybody: the recursion workspace lives in the
+// library image.
+// ---------------------------------------------------------------------------------------
+namespace dat {
+
+constexpr size_t kStaticRowFloats = (size_t)1 << 21;      // 8 MiB of recursion rows
+constexpr size_t kStaticOffsetDoubles = (size_t)1 << 16;  // 512 KiB of row offsets
+
+// One copy per GPU that loads the library, resident until the process exits.  In host code
+// these names are only handles; the device addresses are fetched with cudaGetSymbolAddress.
+static __device__ __align__(256) float g_static_rows[kStaticRowFloats];
+static __device__ __align__(256) double g_static_offsets[kStaticOffsetDoubles];
+
+struct StaticScratch {
+    float *rows;
+    double *offsets;
+    bool ready;
+};
+
+// Device addresses of the static scratch for the CURRENT device (looked up once per device).
+static int static_scratch(StaticScratch *out) {
+    constexpr int kMaxDev = 64;
+    static StaticScratch cache[kMaxDev] = {};
+    static std::mutex mu;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) {
+        cudaGetLastError();
+        set_error("dat_dag_loss_static: no current CUDA device");
+        return DAT_ERR_NO_DEVICE;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cache[dev].ready) {
+        void *rows = nullptr, *offs = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&rows, g_static_rows);
+        if (e == cudaSuccess) e = cudaGetSymbolAddress(&offs, g_static_offsets);
+        if (e != cudaSuccess || !rows || !offs) {
+            cudaGetLastError();
+            set_error("dat_dag_loss_static: cudaGetSymbolAddress failed on device %d: %s", dev,
+                      cudaGetErrorString(e));
+            return DAT_ERR_LAUNCH;
+        }
+        cache[dev].rows = static_cast<float *>(rows);
+        cache[dev].offsets = static_cast<double *>(offs);
+        cache[dev].ready = true;
+    }
+    *out = cache[dev];
+    return DAT_OK;
+}
+
+}  // namespace dat
+
+extern "C" int dat_dag_loss_static(const float *match_all, const float *links,
+                                   const int64_t *output_length, const int64_t *target_length,
+                                   float *loss, int32_t *status, int bsz, int tarlen, int prelen,
+                                   int translen, void *stream) {
+    using namespace dat;
+    DAT_REQUIRE(bsz >= 0 && tarlen >= 1 && prelen >= 1 && translen >= 1, DAT_ERR_BAD_ARG,
+                "dat_dag_loss_static: bad sizes bsz=%d tarlen=%d prelen=%d translen=%d", bsz, tarlen,
+                prelen, translen);
+    if (bsz == 0) return DAT_OK;
+    DAT_REQUIRE(match_all && links && output_length && target_length && loss, DAT_ERR_BAD_ARG,
+                "dat_dag_loss_static: null pointer");
+    const size_t need_rows = (size_t)bsz * tarlen * prelen;
+    const size_t need_offs = (size_t)bsz * (2 * (size_t)tarlen + 2);
+    DAT_REQUIRE(need_rows <= kStaticRowFloats && need_offs <= kStaticOffsetDoubles, DAT_ERR_UNSUPPORTED,
+                "dat_dag_loss_static: bsz*tarlen*prelen = %zu exceeds the built-in workspace of %zu "
+                "floats (or bsz*(2*tarlen+2) = %zu exceeds %zu); use dat_dag_loss with caller-provided "
+                "workspaces for larger batches",
+                need_rows, kStaticRowFloats, need_offs, kStaticOffsetDoubles);
+    DAT_REQUIRE(prelen <= 2 * kSweepThreads, DAT_ERR_UNSUPPORTED,
+                "dat_dag_loss_static: prelen=%d exceeds %d", prelen, 2 * kSweepThreads);
+    DAT_REQUIRE((long long)prelen * translen < (1ll << 31), DAT_ERR_UNSUPPORTED,
+                "dat_dag_loss_static: prelen*translen too large");
+    DeviceInfo di;
+    if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
+    StaticScratch sc;
+    if (int rc = static_scratch(&sc)) return rc;
+    const size_t smem = sweep_smem_bytes(prelen);
+    DAT_REQUIRE(smem <= (size_t)di.max_smem_optin, DAT_ERR_UNSUPPORTED,
+                "dat_dag_loss_static: prelen=%d needs %zu bytes of shared memory", prelen, smem);
+    if (smem > 48 * 1024) {
+        if (cudaFuncSetAttribute(dag_sweep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess)
+            return check_launch("dat_dag_loss_static(attr)");
+    }
+    // alpha sweep only; every row it reads it has written in this launch, so nothing of the
+    // previous call's contents has to be cleared
+    dag_sweep_kernel<<<(unsigned)bsz, kSweepThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        match_all, links, output_length, target_length, sc.rows, nullptr, sc.offsets, loss, status,
+        /*nsweep=*/1, tarlen, prelen, translen);
+    return check_launch("dat_dag_loss_static");
+}

@@ -112,6 +112,28 @@ int dat_dag_loss(const float *match_all, const float *links, const int64_t *outp
                  int bsz, int tarlen, int prelen, int translen, int config, void *stream);
 
 /*
+ * No counterpart in the reference.  Same result as dat_dag_loss(..., require_gradient = 0):
+ * loss[b] = log P(target | graph), but the recursion workspace is a fixed array inside the
+ * library image instead of caller memory, and the call allocates nothing (no cudaMalloc,
+ * no allocating library routine).  It exists for hosts that cannot obtain device memory at
+ * call time: a serving process that gave the whole GPU to its own pool when it started, or a
+ * plugin slot whose contract forbids allocation because cudaMalloc synchronises the device
+ * and would stall the other streams of the process.  Such a host passes only its inputs and
+ * the [bsz] output.
+ * Limits: bsz*tarlen*prelen <= 2^21 floats (8 MiB) and bsz*(2*tarlen+2) <= 2^16; beyond
+ * that the call fails with DAT_ERR_UNSUPPORTED and a message naming both numbers.  Every GPU
+ * that loads the library holds the 8.5 MiB until the process exits.
+ * The first call on a device looks up the array's device address (once per device, with that
+ * device current); make that first call outside any stream capture.
+ * All calls on a device share the one workspace: calls whose kernels overlap on the GPU
+ * (different streams) race on it.  Nothing in it has to be cleared between calls.
+ */
+int dat_dag_loss_static(const float *match_all, const float *links,
+                        const int64_t *output_length, const int64_t *target_length,
+                        float *loss, int32_t *status,
+                        int bsz, int tarlen, int prelen, int translen, void *stream);
+
+/*
  * Replaces `dag_loss_backward` (dag_loss.cpp:20; dag_loss.cu:518-571).
  *   grad_match_all[b,t,j] = g[b] * exp(alpha+beta-match-Z)        (0 where match or Z is +-inf)
  *   grad_links[b,i,d]     = g[b] * sum_t exp(alpha[t,i]+beta[t+1,i+d+1]+links[i,d]-Z)
