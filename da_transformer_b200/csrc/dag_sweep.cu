@@ -327,11 +327,12 @@ __global__ void __launch_bounds__(kSweepThreads)
 dag_sweep_kernel(const float *__restrict__ match, const float *__restrict__ links,
                  const int64_t *__restrict__ output_length, const int64_t *__restrict__ target_length,
                  float *__restrict__ alpha, float *__restrict__ beta, double *__restrict__ offsets,
-                 float *__restrict__ loss, int32_t *__restrict__ status, int nsweep, int T, int L,
-                 int K) {
+                 float *__restrict__ loss, int32_t *__restrict__ status,
+                 const int *__restrict__ select, int nsweep, int T, int L, int K) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int b = blockIdx.x / nsweep;
     const int sweep = blockIdx.x - b * nsweep;
+    if (select != nullptr && select[b] == 0) return;  // sentence already done by the fast path
     const long long ol = output_length[b], tl = target_length[b];
     double *offs = offsets + (size_t)b * (2 * T + 2);
     if (!lengths_valid(ol, tl, T, L)) {
@@ -351,6 +352,28 @@ dag_sweep_kernel(const float *__restrict__ match, const float *__restrict__ link
         beta_sweep(mb, lb, beta + (size_t)b * T * L, offs, loss + b, (int)ol, (int)tl, T, L, K,
                    smem_raw);
     }
+}
+
+// Launches the log-domain sweeps (nsweep = 1: alpha only, 2: alpha and beta).  With a
+// selection mask only the sentences whose entry is non-zero are computed.
+int launch_exact_sweeps(const float *match_all, const float *links, const int64_t *output_length,
+                        const int64_t *target_length, const int *select, float *alpha, float *beta,
+                        double *offsets, float *loss, int32_t *status, int bsz, int tarlen, int prelen,
+                        int translen, int nsweep, cudaStream_t stream, const char *who) {
+    DeviceInfo di;
+    if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
+    const size_t smem = sweep_smem_bytes(prelen);
+    DAT_REQUIRE(smem <= (size_t)di.max_smem_optin, DAT_ERR_UNSUPPORTED,
+                "%s: prelen=%d needs %zu bytes of shared memory", who, prelen, smem);
+    if (smem > 48 * 1024) {
+        if (cudaFuncSetAttribute(dag_sweep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess)
+            return check_launch(who);
+    }
+    dag_sweep_kernel<<<(unsigned)(bsz * nsweep), kSweepThreads, smem, stream>>>(
+        match_all, links, output_length, target_length, alpha, beta, offsets, loss, status, select,
+        nsweep, tarlen, prelen, translen);
+    return check_launch(who);
 }
 
 }  // namespace dat
@@ -380,22 +403,10 @@ int dat_dag_loss(const float *match_all, const float *links, const int64_t *outp
                 "dat_dag_loss: prelen=%d exceeds %d", prelen, 2 * kSweepThreads);
     DAT_REQUIRE((long long)prelen * translen < (1ll << 31), DAT_ERR_UNSUPPORTED,
                 "dat_dag_loss: prelen*translen too large");
-    DeviceInfo di;
-    if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
-    const size_t smem = sweep_smem_bytes(prelen);
-    DAT_REQUIRE(smem <= (size_t)di.max_smem_optin, DAT_ERR_UNSUPPORTED,
-                "dat_dag_loss: prelen=%d needs %zu bytes of shared memory", prelen, smem);
-    if (smem > 48 * 1024) {
-        if (cudaFuncSetAttribute(dag_sweep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem) != cudaSuccess)
-            return check_launch("dat_dag_loss(attr)");
-    }
-    const int nsweep = require_gradient ? 2 : 1;
-    dag_sweep_kernel<<<(unsigned)(bsz * nsweep), kSweepThreads, smem,
-                       static_cast<cudaStream_t>(stream)>>>(
-        match_all, links, output_length, target_length, alpha, beta, offsets, loss, status, nsweep,
-        tarlen, prelen, translen);
-    return check_launch("dat_dag_loss");
+    return launch_exact_sweeps(match_all, links, output_length, target_length, nullptr, alpha, beta,
+                               offsets, loss, status, bsz, tarlen, prelen, translen,
+                               require_gradient ? 2 : 1, static_cast<cudaStream_t>(stream),
+                               "dat_dag_loss");
 }
 
 }  // extern "C"
@@ -490,6 +501,6 @@ extern "C" int dat_dag_loss_static(const float *match_all, const float *links,
     // previous call's contents has to be cleared
     dag_sweep_kernel<<<(unsigned)bsz, kSweepThreads, smem, static_cast<cudaStream_t>(stream)>>>(
         match_all, links, output_length, target_length, sc.rows, nullptr, sc.offsets, loss, status,
-        /*nsweep=*/1, tarlen, prelen, translen);
+        /*select=*/nullptr, /*nsweep=*/1, tarlen, prelen, translen);
     return check_launch("dat_dag_loss_static");
 }

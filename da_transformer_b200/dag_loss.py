@@ -54,7 +54,8 @@ def _status_word(device):
 def last_status(device=None, reset=True):
     """Status bits accumulated on ``device`` since the last reset (synchronises):
     1 = a sentence had invalid lengths, 2 = a sentence had no finite alignment,
-    4 = a gather index was outside the vocabulary."""
+    4 = a gather index was outside the vocabulary, 8 = the fast dag_loss path handed at least
+    one sentence to the exact kernels (informational)."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     buf = _status_word(device)
     value = int(buf.item())
@@ -99,6 +100,10 @@ class DagLossFunc(Function):
     config = 1
     config1 = 2
     config2 = 2
+    # False: when gradients are needed the forward runs the fast probability-domain kernels,
+    # which fall back per sentence to the exact log-domain kernels whenever their dynamic-range
+    # check does not pass.  True: always the exact log-domain kernels.
+    exact = False
 
     @staticmethod
     def forward(ctx, match_all, links, output_length, target_length):
@@ -120,10 +125,18 @@ class DagLossFunc(Function):
             beta = torch.empty(bsz, tarlen, prelen, dtype=torch.float32, device=dev) if require_gradient else None
             offsets = torch.empty(bsz, 2 * tarlen + 2, dtype=torch.float64, device=dev)
             res = torch.empty(bsz, dtype=torch.float32, device=dev)
-            check(L.dat_dag_loss(ptr(match_all), ptr(links), ptr(output_length), ptr(target_length),
-                                 int(require_gradient), ptr(alpha), ptr(beta), ptr(offsets), ptr(res),
-                                 ptr(_status_word(dev)), bsz, tarlen, prelen, translen,
-                                 int(DagLossFunc.config), stream_ptr(dev)), "dag_loss")
+            if require_gradient and not DagLossFunc.exact and bsz > 0:
+                scratch = torch.empty(L.dat_dag_loss_fast_scratch_bytes(bsz, tarlen, prelen),
+                                      dtype=torch.uint8, device=dev)
+                check(L.dat_dag_loss_fast(ptr(match_all), ptr(links), ptr(output_length),
+                                          ptr(target_length), ptr(alpha), ptr(beta), ptr(offsets),
+                                          ptr(res), ptr(_status_word(dev)), ptr(scratch), bsz, tarlen,
+                                          prelen, translen, stream_ptr(dev)), "dag_loss (fast)")
+            else:
+                check(L.dat_dag_loss(ptr(match_all), ptr(links), ptr(output_length), ptr(target_length),
+                                     int(require_gradient), ptr(alpha), ptr(beta), ptr(offsets), ptr(res),
+                                     ptr(_status_word(dev)), bsz, tarlen, prelen, translen,
+                                     int(DagLossFunc.config), stream_ptr(dev)), "dag_loss")
         if require_gradient:
             ctx.save_for_backward(alpha, beta, offsets, match_all, links, output_length, target_length)
         return res

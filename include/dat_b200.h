@@ -50,6 +50,7 @@ enum dat_dtype {
 #define DAT_STATUS_BAD_LENGTH 1 /* a sentence had invalid lengths                  */
 #define DAT_STATUS_NO_PATH 2    /* best alignment: a sentence has no finite path   */
 #define DAT_STATUS_BAD_INDEX 4  /* gather: an index outside [0, vocab)             */
+#define DAT_STATUS_FAST_FALLBACK 8 /* dat_dag_loss_fast recomputed a sentence exactly (informational) */
 
 int dat_version(void);
 const char *dat_last_error(void);
@@ -110,6 +111,24 @@ int dat_dag_loss(const float *match_all, const float *links, const int64_t *outp
                  const int64_t *target_length, int require_gradient,
                  float *alpha, float *beta, double *offsets, float *loss, int32_t *status,
                  int bsz, int tarlen, int prelen, int translen, int config, void *stream);
+
+/*
+ * Fast path of `dag_loss` with require_gradient (replaces the same reference function as
+ * dat_dag_loss: dag_loss.cpp:19; dag_loss.cu:313-375).  Same outputs and the same workspace
+ * format as dat_dag_loss(..., require_gradient = 1, ...), so dat_dag_loss_backward consumes them
+ * unchanged.  The recursions run in the probability domain on E = exp(links), computed once
+ * per call into `scratch` (dat_dag_loss_fast_scratch_bytes bytes, caller-allocated, contents
+ * irrelevant on entry; it also holds what dat_dag_loss_backward_fast reuses).  Per-row
+ * rescaling keeps ~160 binades below each row maximum; an a-posteriori bound on the mass that
+ * could have been flushed decides per sentence whether the result is kept or the sentence is
+ * recomputed by the exact log-domain kernel inside the same call, so the result always meets
+ * the tolerances of dat_dag_loss.
+ */
+size_t dat_dag_loss_fast_scratch_bytes(int bsz, int tarlen, int prelen);
+int dat_dag_loss_fast(const float *match_all, const float *links, const int64_t *output_length,
+                      const int64_t *target_length, float *alpha, float *beta, double *offsets,
+                      float *loss, int32_t *status, void *scratch,
+                      int bsz, int tarlen, int prelen, int translen, void *stream);
 
 /*
  * No counterpart in the reference.  Same result as dat_dag_loss(..., require_gradient = 0):

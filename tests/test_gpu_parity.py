@@ -9,13 +9,22 @@ import pytest
 import torch
 
 from oracle import oracle
-from da_transformer_b200 import (DagBestAlignmentFunc, DagLogsoftmaxGatherFunc, dag_best_alignment,
+from da_transformer_b200 import (DagBestAlignmentFunc, DagLogsoftmaxGatherFunc, DagLossFunc, dag_best_alignment,
                                  dag_logsoftmax_gather_inplace, dag_loss, last_status, workloads)
 from util import assert_rel, assert_rel_quantized, golden
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 TOL_LOSS, TOL_GRAD, TOL_GRAD_HALF, TOL_SEL = 1e-5, 1e-4, 2e-3, 2e-6
+
+
+@pytest.fixture(params=["fast", "exact"], autouse=True)
+def dag_loss_path(request):
+    """Every test runs with the fast (probability-domain, self-checking) forward and with the
+    exact log-domain forward."""
+    DagLossFunc.exact = request.param == "exact"
+    yield request.param
+    DagLossFunc.exact = False
 
 
 def run_dag(match, links, ol, tl, grad_out=None):
@@ -274,9 +283,11 @@ def _properties(batch, grads=True):
     return loss.detach().cpu().numpy(), gm.cpu().numpy(), gl.cpu().numpy(), path
 
 
-def test_properties_at_c4_size_and_oracle_on_a_slice():
+def test_properties_at_c4_size_and_oracle_on_a_slice(dag_loss_path):
     batch = workloads.config4(B=24)
+    last_status()
     loss, gm, gl, path = _properties(batch)
+    assert last_status() & 8 == 0     # no sentence needed the exact fallback
     sl = slice(0, 3)
     rl, rgm, rgl = oracle.dag_loss_fwd_bwd(batch.match_all[sl].numpy(), batch.links[sl].numpy(),
                                            batch.output_length[sl].numpy(), batch.target_length[sl].numpy(),
@@ -362,3 +373,23 @@ def test_empty_batch():
     assert dag_best_alignment(m, l, z, z).shape == (0, 8)
     _, sel = dag_logsoftmax_gather_inplace(torch.empty(0, 8, 5, device=DEV), torch.empty(0, 8, 3, dtype=torch.long, device=DEV))
     assert sel.shape == (0, 8, 3)
+
+
+def test_fast_path_hands_extreme_dynamic_range_to_the_exact_kernels(dag_loss_path):
+    """Inputs whose probabilities leave the fp32 range of the probability-domain recursion
+    (links of -150 nats underflow exp(); match rows spanning hundreds of nats) must still
+    meet the tolerances: the fast path detects them and recomputes those sentences exactly."""
+    batch = workloads.small_batch(seed=61, B=6, L=40, T=7, V=30, ragged=False)
+    links = batch.links.clone()
+    links[0] = torch.where(torch.isfinite(links[0]), torch.full_like(links[0], -150.0), links[0])
+    g = torch.Generator().manual_seed(5)
+    match = batch.match_all.clone()
+    match[1] = torch.randn(match[1].shape, generator=g) * 120.0
+    match[2, 3, :] = -400.0
+    match[2, 3, 17] = 0.0
+    links[3] = torch.where(torch.isfinite(links[3]), links[3] * 12.0, links[3])
+    batch.links, batch.match_all = links, match
+    last_status()
+    check_dag_against_oracle(batch)
+    if dag_loss_path == "fast":
+        assert last_status() & 8
