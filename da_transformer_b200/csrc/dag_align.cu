@@ -3,17 +3,35 @@
 // their host wrapper (fs_plugins/custom_ops/dag_best_alignment.cu:39-130, 170-189,
 // 219-263) and the int32 -> int64 cast of fs_plugins/custom_ops/dag_loss.py:162.
 //
-// One CTA owns one sentence.  Values are the reference's own fp32 sums
-// (alpha[t-1,i] + links[i,d-1], then + match[t,j]), so the maxima are bit-identical; the
-// winner among equal candidates follows the reference's lane scan + shfl_down tree for
-// TRANS_BLOCK_SIZE = 2^lg lanes (dag_best_alignment.cu:96-111): lane = (d-1) mod 2^lg,
-// lanes preferred in bit-reversed order, then the smaller distance d.  That order is a
-// total order on (value, rank), so any reduction tree gives the reference's answer.
+// Values are the reference's own fp32 sums (alpha[t-1,i] + links[i,d-1], then + match[t,j]),
+// so the maxima are bit-identical; the winner among equal candidates follows the
+// reference's lane scan + shfl_down tree for TRANS_BLOCK_SIZE = 2^lg lanes
+// (dag_best_alignment.cu:96-111): lane = (d-1) mod 2^lg, lanes preferred in bit-reversed
+// order, then the smaller distance d.  That order is a total order on (value, rank), so any
+// reduction tree gives the reference's answer.
+//
+// Layout: the band is first copied into a square, 16-byte aligned matrix Lsq[i][j] with
+// -inf everywhere a transition does not exist (dag_align_prep_kernel).  In absolute vertex
+// coordinates -inf replaces all masks (as 0 does in the probability-domain loss kernel), so
+// a warp reads tiles of 16 rows x 128 columns with aligned 128-bit loads and no predicates;
+// each lane owns 4 columns.  Per candidate the common path is 5 instructions (add, two
+// compares, max, select); a chunk in which any lane saw an exact tie is redone with the full
+// tie-break rule.  Warps merge their per-column winners through shared memory with a 64-bit
+// atomicMax on (order-preserving value bits, inverted rank).
+//
+// One CTA owns one sentence; the trace (predecessor distances, uint16) stays in shared
+// memory when it fits, and one thread walks it back at the end of the same launch.
 #include "dag_tiles.cuh"
 
 namespace dat {
 
+constexpr int kAlignThreads = 512;
+constexpr int kAlignWarps = kAlignThreads / 32;
 constexpr int kRankNone = 0x7fffffff;
+constexpr float kNoCand = -3.402823466e+38f;
+
+__host__ __device__ inline int align_pitch(int L) { return (L + 127) & ~127; }
+__host__ __device__ inline int align_rows(int L) { return (L + 15) & ~15; }
 
 __device__ __forceinline__ int tie_rank(int d, int lg) {
     // bit-reversed lane in the high bits, distance in the low 20 bits
@@ -22,25 +40,58 @@ __device__ __forceinline__ int tie_rank(int d, int lg) {
     return (int)((rev << 20) | (unsigned)d);
 }
 
-__device__ __forceinline__ void better(float &bv, int &br, float v, int r) {
-    if (v > bv || (v == bv && r < br && v > -INFINITY)) {
-        bv = v;
-        br = r;
+// order-preserving map float -> uint32 (larger float <=> larger unsigned)
+__device__ __forceinline__ unsigned orderable(float v) {
+    const unsigned u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float unorderable(unsigned o) {
+    return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o);
+}
+__device__ __forceinline__ unsigned long long pack_key(float v, int rank) {
+    v += 0.0f;  // -0.0 and +0.0 compare equal in the reference
+    return ((unsigned long long)orderable(v) << 32) | (unsigned long long)(0xffffffffu - (unsigned)rank);
+}
+
+// square copy of the band, natural-log values, -inf where no transition exists
+__global__ void __launch_bounds__(256)
+dag_align_prep_kernel(const float *__restrict__ links, const int64_t *__restrict__ output_length,
+                      const int64_t *__restrict__ target_length, float *__restrict__ lsq_all, int T,
+                      int L, int K, int rows, int pitch) {
+    const int b = blockIdx.y;
+    const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (i >= rows) return;
+    const long long oll = output_length[b], tll = target_length[b];
+    if (!lengths_valid(oll, tll, T, L)) return;
+    const int ol = (int)oll;
+    const float *brow = links + ((size_t)b * L + (i < L ? i : 0)) * K;
+    float4 *erow = reinterpret_cast<float4 *>(lsq_all + ((size_t)b * rows + i) * pitch);
+    for (int jv = lane; jv < pitch / 4; jv += 32) {
+        float v[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int j = 4 * jv + k;
+            const int d = j - i - 1;
+            const bool ok = i < ol && j < ol && d >= 0 && d < K;
+            v[k] = ok ? __ldg(brow + d) : -INFINITY;
+        }
+        erow[jv] = make_float4(v[0], v[1], v[2], v[3]);
     }
 }
 
 template <bool kTraceInSmem>
-__global__ void __launch_bounds__(kSweepThreads)
-dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ links,
+__global__ void __launch_bounds__(kAlignThreads, 1)
+dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ lsq_all,
                  const int64_t *__restrict__ output_length, const int64_t *__restrict__ target_length,
                  int64_t *__restrict__ path_out, float *__restrict__ max_score,
                  uint16_t *__restrict__ trace_ws, int32_t *__restrict__ status, int T, int L, int K,
-                 int lg) {
+                 int lg, int rows, int pitch) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.x;
     int64_t *path = path_out + (size_t)b * L;
-    for (int j = tid; j < L; j += kSweepThreads) path[j] = -1;
+    for (int j = tid; j < L; j += kAlignThreads) path[j] = -1;
     const long long oll = output_length[b], tll = target_length[b];
     if (!lengths_valid(oll, tll, T, L)) {
         if (tid == 0) {
@@ -52,144 +103,136 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
     const int ol = (int)oll, tl = (int)tll;
     const int W = ol - tl + 1;
     const float *match = match_all + (size_t)b * T * L;
-    const float *band = links + (size_t)b * L * K;
-    const SweepSmem sm = carve(smem_raw, L);
-    // the partial-merge slots hold (value, rank) pairs here
-    int *part_r = reinterpret_cast<int *>(sm.part);
-    int *fin_r = reinterpret_cast<int *>(sm.fin_s);
+    const float *Lsq = lsq_all + (size_t)b * rows * pitch;
+    const int rp = pitch + 32;
+    unsigned long long *skey = reinterpret_cast<unsigned long long *>(smem_raw);  // [pitch]
+    float *rbuf0 = reinterpret_cast<float *>(skey + pitch), *rbuf1 = rbuf0 + rp;
     // trace[t][c]: distance d of the chosen predecessor of window column c at step t (0 = none)
-    uint16_t *trace = kTraceInSmem
-                          ? reinterpret_cast<uint16_t *>(smem_raw + ((sweep_smem_bytes(L) + 15) & ~(size_t)15))
-                          : trace_ws + (size_t)b * T * L;
+    uint16_t *trace = kTraceInSmem ? reinterpret_cast<uint16_t *>(rbuf1 + rp) : trace_ws + (size_t)b * T * L;
     const int tstride = kTraceInSmem ? W : L;
+    const unsigned long long key_none = pack_key(-INFINITY, kRankNone);
 
-    const int pitch = sweep_row_pitch(L);
-    for (int x = tid; x < 2 * pitch; x += kSweepThreads) sm.row0[x] = -INFINITY;  // row0 and row1
-    int my_lo, my_hi, cb_first;
-    build_tile_plan(sm, W, K, my_lo, my_hi, cb_first);
-    // warps without tiles sit between the first and last warp of a shared column block:
-    // their merge slots must read as empty
-#pragma unroll
-    for (int which = 0; which < 2; which++) {
-        const int o = ((which * kSweepWarps + warp) * 2) * 32;
-        sm.part[o + lane] = -INFINITY;
-        part_r[o + 32 + lane] = kRankNone;
-    }
-    if (tid == 0) sm.row0[0] = match[0];
+    for (int x = tid; x < 2 * rp; x += kAlignThreads) rbuf0[x] = -INFINITY;
+    for (int x = tid; x < pitch; x += kAlignThreads) skey[x] = key_none;
+    __syncthreads();
+    if (tid == 0) rbuf0[0] = match[0];
     __syncthreads();
 
-    const unsigned stride = (unsigned)(K - 1);
+    const int ncbmax = pitch >> 7;
     for (int t = 1; t < tl; t++) {
-        const float *prev = (t & 1) ? sm.row0 : sm.row1;  // row of step t-1, window coordinates
-        float *cur = (t & 1) ? sm.row1 : sm.row0;
-        float mt[2];
-#pragma unroll
-        for (int q = 0; q < 2; q++) {
-            int c = tid + q * kSweepThreads;
-            mt[q] = (c < W) ? __ldg(match + (size_t)t * L + t + c) : 0.f;
+        const float *prev = ((t - 1) & 1) ? rbuf1 : rbuf0;  // absolute coordinates, -inf outside the window
+        float *cur = (t & 1) ? rbuf1 : rbuf0;
+        // live region: rows [t-1, t+W-2], columns [t, t+W-1]
+        const int rt_lo = (t - 1) >> 4, rt_hi = (t + W - 2) >> 4;
+        const int cb_lo = t >> 7;
+        int cb_hi = (t + W - 1) >> 7;
+        if (cb_hi > ncbmax - 1) cb_hi = ncbmax - 1;
+        int total = 0;
+        for (int cb = cb_lo; cb <= cb_hi; cb++) {
+            int rf = 128 * cb - K; rf = rf > 0 ? (rf >> 4) : 0; rf = rf > rt_lo ? rf : rt_lo;
+            int rl = 8 * cb + 7; rl = rl < rt_hi ? rl : rt_hi;
+            total += rl >= rf ? rl - rf + 1 : 0;
         }
-        if (my_lo < my_hi) {
-            int cb = cb_first;
-            int rb = sm.rb_lo[cb] + (my_lo - sm.tile_start[cb]);
-            bool owns_start = (my_lo == sm.tile_start[cb]);
-            float bv = -INFINITY;
-            int br = kRankNone;
-            const unsigned row_base = (unsigned)(t - 1) * (unsigned)K;
-            for (int tile = my_lo; tile < my_hi;) {
-                const TileGeom g = tile_geom(cb, rb, lane, W, K);
-                const unsigned off0 = row_base + (unsigned)g.c;
-                if (g.interior) {
-#pragma unroll 1
-                    for (int r = g.r0; r < g.r0 + 32; r += kChunk) {
-                        const float4 p0 = *reinterpret_cast<const float4 *>(prev + r);
-                        const float4 p1 = *reinterpret_cast<const float4 *>(prev + r + 4);
-                        const float pa[kChunk] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-                        const unsigned o = off0 + (unsigned)r * stride;
-                        float x[kChunk];
+        const int my_lo = (warp * total) / kAlignWarps, my_hi = ((warp + 1) * total) / kAlignWarps;
+        const bool reverse = t & 1;
+        int base = 0;
+        for (int cbx = cb_lo; cbx <= cb_hi; cbx++) {
+            const int cb = reverse ? (cb_hi - (cbx - cb_lo)) : cbx;
+            int rf = 128 * cb - K; rf = rf > 0 ? (rf >> 4) : 0; rf = rf > rt_lo ? rf : rt_lo;
+            int rl = 8 * cb + 7; rl = rl < rt_hi ? rl : rt_hi;
+            const int n = rl >= rf ? rl - rf + 1 : 0;
+            const int from = my_lo > base ? my_lo - base : 0;
+            const int to = my_hi < base + n ? my_hi - base : n;
+            base += n;
+            if (from >= to) continue;
+            const int col = 128 * cb + 4 * lane;
+            // "nothing yet" is the most negative finite float rather than -inf, so that the
+            // -inf of non-existent transitions never compares equal to it (no false ties)
+            float bv[4] = {kNoCand, kNoCand, kNoCand, kNoCand};
+            int bi[4] = {-1, -1, -1, -1};
+            for (int q = from; q < to; q++) {
+                const int rt = reverse ? (rl - q) : (rf + q);
 #pragma unroll
-                        for (int u = 0; u < kChunk; u++) x[u] = __ldg(band + (o + (unsigned)u * stride));
+                for (int h = 0; h < 2; h++) {
+                    const int i0 = 16 * rt + 8 * h;
+                    const float4 *ep = reinterpret_cast<const float4 *>(Lsq + (size_t)i0 * pitch + col);
+                    float4 e[8];
 #pragma unroll
-                        for (int u = 0; u < kChunk; u++) x[u] = __fadd_rn(pa[u], x[u]);
-                        float cm = x[0];
+                    for (int r = 0; r < 8; r++) e[r] = __ldg(ep + (size_t)r * (pitch >> 2));
+                    const float4 a0 = *reinterpret_cast<const float4 *>(prev + i0);
+                    const float4 a1 = *reinterpret_cast<const float4 *>(prev + i0 + 4);
+                    const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                    const float sv[4] = {bv[0], bv[1], bv[2], bv[3]};
+                    const int si[4] = {bi[0], bi[1], bi[2], bi[3]};
+                    bool tie = false;
 #pragma unroll
-                        for (int u = 1; u < kChunk; u++) cm = fmaxf(cm, x[u]);
-                        if (cm >= bv && cm > -INFINITY) {  // some candidate of the chunk may win or tie
+                    for (int r = 0; r < 8; r++) {
+                        const float v[4] = {__fadd_rn(av[r], e[r].x), __fadd_rn(av[r], e[r].y),
+                                            __fadd_rn(av[r], e[r].z), __fadd_rn(av[r], e[r].w)};
 #pragma unroll
-                            for (int u = 0; u < kChunk; u++)
-                                if (x[u] >= bv) better(bv, br, x[u], tie_rank(g.c - (r + u) + 1, lg));
+                        for (int k = 0; k < 4; k++) {
+                            tie |= (v[k] == bv[k]);
+                            const bool up = v[k] > bv[k];
+                            bv[k] = up ? v[k] : bv[k];
+                            bi[k] = up ? (i0 + r) : bi[k];
                         }
                     }
-                } else {
-#pragma unroll 1
-                    for (int r = g.r0; r < g.r1; r += kChunk) {
-                        float x[kChunk];
+                    if (__any_sync(0xffffffffu, tie)) {
+                        // redo the chunk with the reference's full tie-break
 #pragma unroll
-                        for (int u = 0; u < kChunk; u++) {
-                            const int rr = r + u;
-                            const bool ok = (rr >= g.rmin) && (rr <= g.rmax);
-                            const float lk = ok ? __ldg(band + (off0 + (unsigned)rr * stride)) : -INFINITY;
-                            x[u] = __fadd_rn(prev[rr], lk);  // rows past the window read the -inf padding
+                        for (int k = 0; k < 4; k++) { bv[k] = sv[k]; bi[k] = si[k]; }
+#pragma unroll
+                        for (int r = 0; r < 8; r++) {
+                            const float v[4] = {__fadd_rn(av[r], e[r].x), __fadd_rn(av[r], e[r].y),
+                                                __fadd_rn(av[r], e[r].z), __fadd_rn(av[r], e[r].w)};
+#pragma unroll
+                            for (int k = 0; k < 4; k++) {
+                                const int j = col + k, i = i0 + r;
+                                bool up = v[k] > bv[k];
+                                if (!up && v[k] == bv[k] && v[k] > -INFINITY && j > i) {
+                                    const int rnew = tie_rank(j - i, lg);
+                                    const int rold = bi[k] >= 0 ? tie_rank(j - bi[k], lg) : kRankNone;
+                                    up = rnew < rold;
+                                }
+                                if (up) { bv[k] = v[k]; bi[k] = i; }
+                            }
                         }
+                    }
+                }
+            }
 #pragma unroll
-                        for (int u = 0; u < kChunk; u++)
-                            if (x[u] >= bv && x[u] > -INFINITY)
-                                better(bv, br, x[u], tie_rank(g.c - (r + u) + 1, lg));
-                    }
-                }
-                tile++;
-                rb++;
-                if (rb > cb || tile == my_hi) {
-                    const bool complete = owns_start && (rb > cb);
-                    if (complete) {
-                        if (g.c < W) { sm.fin_m[g.c] = bv; fin_r[g.c] = br; }
-                    } else {
-                        const int which = (cb == cb_first) ? 0 : 1;
-                        const int o = ((which * kSweepWarps + warp) * 2) * 32;
-                        sm.part[o + lane] = bv;
-                        part_r[o + 32 + lane] = br;
-                    }
-                    cb++;
-                    rb = sm.rb_lo[cb];
-                    owns_start = true;
-                    bv = -INFINITY;
-                    br = kRankNone;
-                }
+            for (int k = 0; k < 4; k++) {
+                const int rank = (bi[k] >= 0) ? tie_rank(col + k - bi[k], lg) : kRankNone;
+                if (rank != kRankNone) atomicMax(skey + col + k, pack_key(bv[k], rank));
             }
         }
         __syncthreads();
-#pragma unroll
-        for (int q = 0; q < 2; q++) {
-            const int c = tid + q * kSweepThreads;
-            if (c < W) {
-                const int cb = c >> 5, ln = c & 31;
-                const int wa = sm.first_warp[cb], wb = sm.last_warp[cb];
-                float bv;
-                int br;
-                if (wa == wb) {
-                    bv = sm.fin_m[c];
-                    br = fin_r[c];
-                } else {
-                    bv = -INFINITY;
-                    br = kRankNone;
-                    for (int w = wa; w <= wb; w++) {
-                        const int which = (sm.cb_first_of[w] == cb) ? 0 : 1;
-                        const int o = ((which * kSweepWarps + w) * 2) * 32;
-                        better(bv, br, sm.part[o + ln], part_r[o + 32 + ln]);
-                    }
-                }
-                float v = __fadd_rn(bv, mt[q]);
-                if (!(v > -INFINITY)) v = -INFINITY;  // keeps the -inf padding convention under NaN
-                cur[c] = v;
-                const int d = (br == kRankNone) ? 0 : (br & 0xfffff);
-                trace[(size_t)t * tstride + (kTraceInSmem ? c : (t + c))] = (uint16_t)d;
+
+        // finalisation: consume and clear every merge slot that may have been touched
+        for (int j = 128 * cb_lo + tid; j < 128 * (cb_hi + 1); j += kAlignThreads) {
+            const unsigned long long key = skey[j];
+            skey[j] = key_none;
+            const int c = j - t;
+            if (c >= 0 && c < W) {
+                const float best = unorderable((unsigned)(key >> 32));
+                const int rank = (int)(0xffffffffu - (unsigned)(key & 0xffffffffu));
+                float v = __fadd_rn(best, __ldg(match + (size_t)t * L + j));
+                if (!(v > -INFINITY)) v = -INFINITY;
+                cur[j] = v;
+                const int d = (rank == kRankNone) ? 0 : (rank & 0xfffff);
+                trace[(size_t)t * tstride + (kTraceInSmem ? c : j)] = (uint16_t)d;
             }
+        }
+        if (tid == 0) {  // entries of the recycled row buffer that left the window
+            cur[t - 1] = -INFINITY;
+            if (t >= 2) cur[t - 2] = -INFINITY;
         }
         __syncthreads();
     }
 
     // backtrace (dag_best_alignment.cu:185-188), one thread
     if (tid == 0) {
-        const float score = (((tl - 1) & 1) ? sm.row1 : sm.row0)[W - 1];
+        const float score = (((tl - 1) & 1) ? rbuf1 : rbuf0)[ol - 1];
         if (max_score) max_score[b] = score;
         if (score > -INFINITY) {
             int pos = ol - 1;
@@ -208,9 +251,12 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
     }
 }
 
-static inline size_t align_trace_smem(int T, int L) {
-    // worst case window W = L - 2 + 1
-    return (size_t)T * (size_t)L * sizeof(uint16_t);
+static inline size_t align_base_smem(int L) {
+    const int pitch = align_pitch(L);
+    return (size_t)pitch * 8 + (size_t)2 * (pitch + 32) * 4;
+}
+static inline size_t align_lsq_bytes(int B, int L) {
+    return (((size_t)B * align_rows(L) * align_pitch(L) * sizeof(float)) + 255) & ~(size_t)255;
 }
 
 }  // namespace dat
@@ -218,8 +264,9 @@ static inline size_t align_trace_smem(int T, int L) {
 extern "C" {
 
 size_t dat_dag_best_alignment_workspace_bytes(int bsz, int tarlen, int prelen) {
-    if (bsz < 0 || tarlen < 0 || prelen < 0) return 0;
-    return (size_t)bsz * tarlen * prelen * sizeof(uint16_t) + 16;
+    if (bsz <= 0 || tarlen <= 0 || prelen <= 0) return 0;
+    // square copy of the links + (only used when it does not fit in shared memory) the trace
+    return dat::align_lsq_bytes(bsz, prelen) + (size_t)bsz * tarlen * prelen * sizeof(uint16_t) + 512;
 }
 
 int dat_dag_best_alignment(const float *match_all, const float *links,
@@ -234,37 +281,42 @@ int dat_dag_best_alignment(const float *match_all, const float *links,
     DAT_REQUIRE(config >= 1 && config <= 4, DAT_ERR_BAD_ARG,
                 "dat_dag_best_alignment: config should be 1~4 (got %d)", config);
     if (bsz == 0) return DAT_OK;
-    DAT_REQUIRE(match_all && links && output_length && target_length && path, DAT_ERR_BAD_ARG,
-                "dat_dag_best_alignment: null pointer");
-    DAT_REQUIRE(prelen <= 2 * kSweepThreads, DAT_ERR_UNSUPPORTED,
-                "dat_dag_best_alignment: prelen=%d exceeds %d", prelen, 2 * kSweepThreads);
+    DAT_REQUIRE(match_all && links && output_length && target_length && path && workspace,
+                DAT_ERR_BAD_ARG, "dat_dag_best_alignment: null pointer");
+    DAT_REQUIRE(prelen <= 65535, DAT_ERR_UNSUPPORTED,
+                "dat_dag_best_alignment: prelen=%d exceeds 65535", prelen);
     DeviceInfo di;
     if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
     const int lg = config + 1;  // 4, 8, 16, 32 lanes
-    const size_t base = (sweep_smem_bytes(prelen) + 15) & ~(size_t)15;
-    const size_t with_trace = base + align_trace_smem(tarlen, prelen);
+    const int rows = align_rows(prelen), pitch = align_pitch(prelen);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uintptr_t wbase = (reinterpret_cast<uintptr_t>(workspace) + 255) & ~(uintptr_t)255;
+    float *lsq = reinterpret_cast<float *>(wbase);
+    uint16_t *trace_ws = reinterpret_cast<uint16_t *>(wbase + align_lsq_bytes(bsz, prelen));
+    {
+        dim3 grid((rows + 7) / 8, bsz);
+        dag_align_prep_kernel<<<grid, 256, 0, st>>>(links, output_length, target_length, lsq, tarlen,
+                                                    prelen, translen, rows, pitch);
+        if (int rc = check_launch("dat_dag_best_alignment(prep)")) return rc;
+    }
+    const size_t base = (align_base_smem(prelen) + 15) & ~(size_t)15;
+    DAT_REQUIRE(base <= (size_t)di.max_smem_optin, DAT_ERR_UNSUPPORTED,
+                "dat_dag_best_alignment: prelen=%d needs %zu bytes of shared memory", prelen, base);
+    const size_t with_trace = base + (size_t)tarlen * prelen * sizeof(uint16_t);
     if (with_trace <= (size_t)di.max_smem_optin) {
         if (cudaFuncSetAttribute(dag_align_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)with_trace) != cudaSuccess)
             return check_launch("dat_dag_best_alignment(attr)");
-        dag_align_kernel<true><<<(unsigned)bsz, kSweepThreads, with_trace, st>>>(
-            match_all, links, output_length, target_length, path, max_score, nullptr, status,
-            tarlen, prelen, translen, lg);
+        dag_align_kernel<true><<<(unsigned)bsz, kAlignThreads, with_trace, st>>>(
+            match_all, lsq, output_length, target_length, path, max_score, nullptr, status, tarlen,
+            prelen, translen, lg, rows, pitch);
     } else {
-        DAT_REQUIRE(workspace != nullptr, DAT_ERR_BAD_ARG,
-                    "dat_dag_best_alignment: workspace required for tarlen=%d prelen=%d", tarlen,
-                    prelen);
-        DAT_REQUIRE(base <= (size_t)di.max_smem_optin, DAT_ERR_UNSUPPORTED,
-                    "dat_dag_best_alignment: prelen=%d too large", prelen);
         if (cudaFuncSetAttribute(dag_align_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)base) != cudaSuccess)
             return check_launch("dat_dag_best_alignment(attr)");
-        uint16_t *ws = reinterpret_cast<uint16_t *>(
-            (reinterpret_cast<uintptr_t>(workspace) + 15) & ~(uintptr_t)15);
-        dag_align_kernel<false><<<(unsigned)bsz, kSweepThreads, base, st>>>(
-            match_all, links, output_length, target_length, path, max_score, ws, status, tarlen,
-            prelen, translen, lg);
+        dag_align_kernel<false><<<(unsigned)bsz, kAlignThreads, base, st>>>(
+            match_all, lsq, output_length, target_length, path, max_score, trace_ws, status, tarlen,
+            prelen, translen, lg, rows, pitch);
     }
     return check_launch("dat_dag_best_alignment");
 }

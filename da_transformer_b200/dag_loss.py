@@ -182,12 +182,9 @@ class DagBestAlignmentFunc(Function):
         L = lib()
         with torch.cuda.device(dev):
             path = torch.empty(bsz, prelen, dtype=torch.long, device=dev)
+            # square copy of the links (+ room for the trace when it does not fit on chip)
             nbytes = L.dat_dag_best_alignment_workspace_bytes(bsz, tarlen, prelen)
-            ws = None
-            # the trace stays in shared memory when it fits (T*L*2 bytes + row buffers);
-            # the library makes the exact decision, this only avoids a needless allocation
-            if 2 * tarlen * prelen + 16 * prelen + 16384 > 200 * 1024:
-                ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+            ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
             check(L.dat_dag_best_alignment(
                 ptr(match_all), ptr(links), ptr(output_length), ptr(target_length), ptr(path),
                 ptr(None), ptr(ws), ptr(_status_word(dev)), bsz, tarlen, prelen, translen,
