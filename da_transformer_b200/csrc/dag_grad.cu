@@ -55,10 +55,11 @@ __global__ void __launch_bounds__(kGlThreads)
 dag_grad_links_kernel(const float *__restrict__ grad_out, const float *__restrict__ alpha,
                       const float *__restrict__ beta, const double *__restrict__ offsets,
                       const float *__restrict__ links, const int64_t *__restrict__ output_length,
-                      const int64_t *__restrict__ target_length, float *__restrict__ glinks, int T,
-                      int L, int K) {
+                      const int64_t *__restrict__ target_length, float *__restrict__ glinks,
+                      const int *__restrict__ select, int T, int L, int K) {
     extern __shared__ __align__(16) float a_s[];  // [T][kGlRows]: alpha2[t,i] + k_t, -inf when dead
     const int b = blockIdx.y;
+    if (select != nullptr && select[b] == 0) return;  // done by the product-form kernel
     const int i0 = blockIdx.x * kGlRows;
     const int tid = threadIdx.x;
     const long long oll = output_length[b], tll = target_length[b];
@@ -136,6 +137,35 @@ dag_grad_links_kernel(const float *__restrict__ grad_out, const float *__restric
 
 }  // namespace dat
 
+namespace dat {
+
+int launch_grad_match(const float *grad_output, const float *alpha, const float *beta,
+                      const double *offsets, const float *match_all, const int64_t *output_length,
+                      const int64_t *target_length, float *grad_match_all, int bsz, int tarlen,
+                      int prelen, cudaStream_t st, const char *who) {
+    dim3 grid((prelen + 255) / 256, tarlen, bsz);
+    dag_grad_match_kernel<<<grid, 256, 0, st>>>(grad_output, alpha, beta, offsets, match_all,
+                                                output_length, target_length, grad_match_all, tarlen,
+                                                prelen);
+    return check_launch(who);
+}
+
+// exact grad_links; with a selection mask only the sentences whose entry is non-zero
+int launch_exact_grad_links(const float *grad_output, const float *alpha, const float *beta,
+                            const double *offsets, const float *links, const int64_t *output_length,
+                            const int64_t *target_length, float *grad_links, const int *select, int bsz,
+                            int tarlen, int prelen, int translen, cudaStream_t st, const char *who) {
+    const size_t smem = (size_t)tarlen * kGlRows * sizeof(float);
+    DAT_REQUIRE(smem <= 48 * 1024, DAT_ERR_UNSUPPORTED, "%s: tarlen=%d too large", who, tarlen);
+    dim3 grid((prelen + kGlRows - 1) / kGlRows, bsz);
+    dag_grad_links_kernel<<<grid, kGlThreads, smem, st>>>(grad_output, alpha, beta, offsets, links,
+                                                         output_length, target_length, grad_links, select,
+                                                         tarlen, prelen, translen);
+    return check_launch(who);
+}
+
+}  // namespace dat
+
 extern "C" {
 
 int dat_dag_loss_backward(const float *grad_output, const float *alpha, const float *beta,
@@ -156,24 +186,13 @@ int dat_dag_loss_backward(const float *grad_output, const float *alpha, const fl
     DAT_REQUIRE(bsz <= 65535 && tarlen <= 65535, DAT_ERR_UNSUPPORTED,
                 "dat_dag_loss_backward: bsz and tarlen are limited to 65535");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    {
-        dim3 grid((prelen + 255) / 256, tarlen, bsz);
-        dag_grad_match_kernel<<<grid, 256, 0, st>>>(grad_output, alpha, beta, offsets, match_all,
-                                                    output_length, target_length, grad_match_all,
-                                                    tarlen, prelen);
-        int rc = check_launch("dat_dag_loss_backward(grad_match)");
-        if (rc) return rc;
-    }
-    {
-        const size_t smem = (size_t)tarlen * kGlRows * sizeof(float);
-        DAT_REQUIRE(smem <= 48 * 1024, DAT_ERR_UNSUPPORTED,
-                    "dat_dag_loss_backward: tarlen=%d too large", tarlen);
-        dim3 grid((prelen + kGlRows - 1) / kGlRows, bsz);
-        dag_grad_links_kernel<<<grid, kGlThreads, smem, st>>>(grad_output, alpha, beta, offsets,
-                                                             links, output_length, target_length,
-                                                             grad_links, tarlen, prelen, translen);
-        return check_launch("dat_dag_loss_backward(grad_links)");
-    }
+    if (int rc = launch_grad_match(grad_output, alpha, beta, offsets, match_all, output_length,
+                                   target_length, grad_match_all, bsz, tarlen, prelen, st,
+                                   "dat_dag_loss_backward(grad_match)"))
+        return rc;
+    return launch_exact_grad_links(grad_output, alpha, beta, offsets, links, output_length,
+                                   target_length, grad_links, nullptr, bsz, tarlen, prelen, translen, st,
+                                   "dat_dag_loss_backward(grad_links)");
 }
 
 }  // extern "C"

@@ -125,6 +125,7 @@ class DagLossFunc(Function):
             beta = torch.empty(bsz, tarlen, prelen, dtype=torch.float32, device=dev) if require_gradient else None
             offsets = torch.empty(bsz, 2 * tarlen + 2, dtype=torch.float64, device=dev)
             res = torch.empty(bsz, dtype=torch.float32, device=dev)
+            scratch = None
             if require_gradient and not DagLossFunc.exact and bsz > 0:
                 scratch = torch.empty(L.dat_dag_loss_fast_scratch_bytes(bsz, tarlen, prelen),
                                       dtype=torch.uint8, device=dev)
@@ -139,6 +140,7 @@ class DagLossFunc(Function):
                                      int(DagLossFunc.config), stream_ptr(dev)), "dag_loss")
         if require_gradient:
             ctx.save_for_backward(alpha, beta, offsets, match_all, links, output_length, target_length)
+            ctx.fast_scratch = scratch   # exp(links) + per-sentence flags, reused by the backward
         return res
 
     @staticmethod
@@ -153,11 +155,18 @@ class DagLossFunc(Function):
         with torch.cuda.device(dev):
             grad_match_all = torch.empty_like(match_all)
             grad_links = torch.empty_like(links)
-            check(lib().dat_dag_loss_backward(
-                ptr(grad_output), ptr(alpha), ptr(beta), ptr(offsets), ptr(match_all), ptr(links),
-                ptr(output_length), ptr(target_length), ptr(grad_match_all), ptr(grad_links),
-                bsz, tarlen, prelen, translen, int(DagLossFunc.config1), int(DagLossFunc.config2),
-                stream_ptr(dev)), "dag_loss_backward")
+            if ctx.fast_scratch is not None:
+                check(lib().dat_dag_loss_backward_fast(
+                    ptr(grad_output), ptr(alpha), ptr(beta), ptr(offsets), ptr(match_all), ptr(links),
+                    ptr(output_length), ptr(target_length), ptr(grad_match_all), ptr(grad_links),
+                    ptr(ctx.fast_scratch), bsz, tarlen, prelen, translen, stream_ptr(dev)),
+                    "dag_loss_backward (fast)")
+            else:
+                check(lib().dat_dag_loss_backward(
+                    ptr(grad_output), ptr(alpha), ptr(beta), ptr(offsets), ptr(match_all), ptr(links),
+                    ptr(output_length), ptr(target_length), ptr(grad_match_all), ptr(grad_links),
+                    bsz, tarlen, prelen, translen, int(DagLossFunc.config1), int(DagLossFunc.config2),
+                    stream_ptr(dev)), "dag_loss_backward")
         return grad_match_all, grad_links, None, None
 
 

@@ -131,6 +131,19 @@ int dat_dag_loss_fast(const float *match_all, const float *links, const int64_t 
                       int bsz, int tarlen, int prelen, int translen, void *stream);
 
 /*
+ * Backward for a forward done by dat_dag_loss_fast (replaces dag_loss_backward, dag_loss.cpp:20;
+ * dag_loss.cu:518-571, like dat_dag_loss_backward).  `scratch` is the forward's scratch,
+ * untouched since.  grad_links is computed in product form (one exp per stored row entry, then
+ * a small matrix product over the target steps) for the sentences that passed the forward's
+ * dynamic-range check and by the exact kernel for the others.
+ */
+int dat_dag_loss_backward_fast(const float *grad_output, const float *alpha, const float *beta,
+                               const double *offsets, const float *match_all, const float *links,
+                               const int64_t *output_length, const int64_t *target_length,
+                               float *grad_match_all, float *grad_links, const void *scratch,
+                               int bsz, int tarlen, int prelen, int translen, void *stream);
+
+/*
  * No counterpart in the reference.  Same result as dat_dag_loss(..., require_gradient = 0):
  * loss[b] = log P(target | graph), but the recursion workspace is a fixed array inside the
  * library image instead of caller memory, and the call allocates nothing (no cudaMalloc,
