@@ -14,8 +14,11 @@ The inputs (600 MB per GPU) are larger than L2, so no flush is needed between st
 `value` is sentences/s with the inputs resident in HBM; `e2e` is the same step through
 the public Python API with inputs copied from pinned host memory and the statistics
 copied back every step.  `roofline` describes the dominant kernel (the alpha/beta sweep):
-algorithmic special-function evaluations per launch over its CUDA-event duration, against
-the special-function throughput measured on this device just before.  `gather` reports
+algorithmic special-function evaluations per launch (one exp per (t, i->j) term of the
+log-domain recursion, the reference's formulation) over its CUDA-event duration, against
+the special-function throughput measured on this device just before.  The shipped forward
+runs the recursion in the probability domain and spends one FFMA per term instead, so the
+fraction may exceed 1.  `gather` reports
 logsoftmax_gather forward+backward on the C2 shape against the measured HBM copy
 bandwidth.  `cpu_baseline` is the CPU oracle (a port of the reference's arithmetic) timed
 on this host's cores on a bounded sample.
@@ -405,9 +408,12 @@ def main():
         },
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": 4 * args.steps,
+        # per step: alignment (square copy + sweep), loss forward (order, exp(links), fused sweep, check,
+        # exact fallback), loss backward (grad_match, product-form grad_links, exact fallback)
+        "gpu_launches": 10 * args.steps,
         "roofline": {
-            "kernel": "dag_sweep_kernel (alpha+beta recursions, one launch per step)",
+            "kernel": ("dag_loss forward = dag_fast_sweep_kernel (fused alpha+beta recursion) with its "
+                       "exp(links) preparation, check and fallback launches"),
             "bound": "mufu", "achieved": sweep_rate / 1e9, "peak": mufu_peak / 1e9, "unit": "Gexp/s",
             "frac": sweep_rate / mufu_peak, "traffic": None,
             "peak_kind": "measured on this device by dat_probe_mufu just before the timed region",
