@@ -16,6 +16,10 @@ namespace dat {
 
 constexpr int kLsgThreads = 256;
 constexpr int kLsgWarps = kLsgThreads / 32;
+#ifndef DAT_BWD_UNROLL
+#define DAT_BWD_UNROLL 4
+#endif
+constexpr int kBwdUnroll = DAT_BWD_UNROLL;  // 16-byte vectors in flight per thread in the backward
 
 struct Strides3 {
     int64_t b, l, s;
@@ -201,16 +205,18 @@ lsg_bwd_kernel(T *__restrict__ x, const int64_t *__restrict__ idx, Strides3 is,
         const float c = -(M + logS) * kLog2e;
         const float nG = -G;
         int v = tid;
-        for (; v + kLsgThreads < nvec; v += 2 * kLsgThreads) {
-            uint4 u0 = xv[v];
-            uint4 u1 = xv[v + kLsgThreads];
-            float f[2 * kVec];
-            Elem<T>::unpack(u0, f);
-            Elem<T>::unpack(u1, f + kVec);
+        for (; v + (kBwdUnroll - 1) * kLsgThreads < nvec; v += kBwdUnroll * kLsgThreads) {
+            uint4 u[kBwdUnroll];
 #pragma unroll
-            for (int i = 0; i < 2 * kVec; i++) f[i] = nG * ex2(fmaf(f[i], kLog2e, c));
-            xv[v] = Elem<T>::pack(f);
-            xv[v + kLsgThreads] = Elem<T>::pack(f + kVec);
+            for (int q = 0; q < kBwdUnroll; q++) u[q] = xv[v + q * kLsgThreads];
+#pragma unroll
+            for (int q = 0; q < kBwdUnroll; q++) {
+                float f[kVec];
+                Elem<T>::unpack(u[q], f);
+#pragma unroll
+                for (int i = 0; i < kVec; i++) f[i] = nG * ex2(fmaf(f[i], kLog2e, c));
+                xv[v + q * kLsgThreads] = Elem<T>::pack(f);
+            }
         }
         for (; v < nvec; v += kLsgThreads) {
             uint4 u0 = xv[v];
