@@ -135,6 +135,13 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
         }
         const int my_lo = (warp * total) / kAlignWarps, my_hi = ((warp + 1) * total) / kAlignWarps;
         const bool reverse = t & 1;
+        // match values of the columns this thread finalises, requested before the tile phase
+        float mp[2];
+#pragma unroll
+        for (int q = 0; q < 2; q++) {
+            const int j = 128 * cb_lo + tid + q * kAlignThreads, c = j - t;
+            mp[q] = (c >= 0 && c < W) ? __ldg(match + (size_t)t * L + j) : 0.f;
+        }
         int base = 0;
         for (int cbx = cb_lo; cbx <= cb_hi; cbx++) {
             const int cb = reverse ? (cb_hi - (cbx - cb_lo)) : cbx;
@@ -209,14 +216,16 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
         __syncthreads();
 
         // finalisation: consume and clear every merge slot that may have been touched
-        for (int j = 128 * cb_lo + tid; j < 128 * (cb_hi + 1); j += kAlignThreads) {
+        int fq = 0;
+        for (int j = 128 * cb_lo + tid; j < 128 * (cb_hi + 1); j += kAlignThreads, fq++) {
             const unsigned long long key = skey[j];
             skey[j] = key_none;
             const int c = j - t;
             if (c >= 0 && c < W) {
                 const float best = unorderable((unsigned)(key >> 32));
                 const int rank = (int)(0xffffffffu - (unsigned)(key & 0xffffffffu));
-                float v = __fadd_rn(best, __ldg(match + (size_t)t * L + j));
+                const float mt = fq == 0 ? mp[0] : (fq == 1 ? mp[1] : __ldg(match + (size_t)t * L + j));
+                float v = __fadd_rn(best, mt);
                 if (!(v > -INFINITY)) v = -INFINITY;
                 cur[j] = v;
                 const int d = (rank == kRankNone) ? 0 : (rank & 0xfffff);

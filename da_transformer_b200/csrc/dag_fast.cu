@@ -278,6 +278,15 @@ dag_fast_sweep_kernel(const float *__restrict__ match_all, const float *__restri
         }
         const int my_lo = (warp * total) / kFastWarps, my_hi = ((warp + 1) * total) / kFastWarps;
         const bool reverse = k & 1;
+        // match values of the entries this thread finalises, requested before the tile phase
+        float mpa[2], mpb[2];
+#pragma unroll
+        for (int q = 0; q < 2; q++) {
+            const int j = 128 * cb_lo + tid + q * kFastThreads, c = j - ta;
+            mpa[q] = (c >= 0 && c < W) ? __ldg(match + (size_t)ta * L + j) : 0.f;
+            const int i = 16 * rt_lo + tid + q * kFastThreads, r = i - tb;
+            mpb[q] = (r >= 0 && r < W) ? __ldg(match + (size_t)tb * L + i) : 0.f;
+        }
         int base = 0;
         for (int cbx = cb_lo; cbx <= cb_hi; cbx++) {
             // walk column blocks in the same direction as the rows so the whole order flips
@@ -292,29 +301,42 @@ dag_fast_sweep_kernel(const float *__restrict__ match_all, const float *__restri
             const int col = 128 * cb + 4 * lane;
             const float4 b4 = *reinterpret_cast<const float4 *>(b_next + col);
             float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+            // does this column block meet the alpha / beta region at all (warp-uniform)
+            const bool cols_a = (128 * cb + 127 >= xa + 1) && (128 * cb <= xa + W);
+            const bool cols_b = (128 * cb + 127 >= xb + 1) && (128 * cb <= xb + W);
             for (int q = from; q < to; q++) {
                 const int rt = reverse ? (rl - q) : (rf + q);
 #pragma unroll
                 for (int h = 0; h < 2; h++) {
                     const int i0 = 16 * rt + 8 * h;
+                    // a half-tile outside a sweep's region only multiplies zeros for that sweep
+                    const bool live_a = cols_a && (i0 + 7 >= xa) && (i0 <= xa + W - 1);
+                    const bool live_b = cols_b && (i0 + 7 >= xb) && (i0 <= xb + W - 1);
+                    if (!live_a && !live_b) continue;
                     const float4 *ep = reinterpret_cast<const float4 *>(E + (size_t)i0 * pitch + col);
                     float4 e[8];
 #pragma unroll
                     for (int r = 0; r < 8; r++) e[r] = __ldg(ep + (size_t)r * (pitch >> 2));
-                    const float4 a0 = *reinterpret_cast<const float4 *>(a_prev + i0);
-                    const float4 a1 = *reinterpret_cast<const float4 *>(a_prev + i0 + 4);
-                    const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                    float rpart[8];
+                    if (live_a) {
+                        const float4 a0 = *reinterpret_cast<const float4 *>(a_prev + i0);
+                        const float4 a1 = *reinterpret_cast<const float4 *>(a_prev + i0 + 4);
+                        const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
 #pragma unroll
-                    for (int r = 0; r < 8; r++) {
-                        acc0 = fmaf(av[r], e[r].x, acc0);
-                        acc1 = fmaf(av[r], e[r].y, acc1);
-                        acc2 = fmaf(av[r], e[r].z, acc2);
-                        acc3 = fmaf(av[r], e[r].w, acc3);
-                        rpart[r] = fmaf(e[r].w, b4.w, fmaf(e[r].z, b4.z, fmaf(e[r].y, b4.y, e[r].x * b4.x)));
+                        for (int r = 0; r < 8; r++) {
+                            acc0 = fmaf(av[r], e[r].x, acc0);
+                            acc1 = fmaf(av[r], e[r].y, acc1);
+                            acc2 = fmaf(av[r], e[r].z, acc2);
+                            acc3 = fmaf(av[r], e[r].w, acc3);
+                        }
                     }
-                    const float tot = reduce8_transposed(rpart, lane);
-                    if ((lane & 3) == 0) atomicAdd(sb + i0 + ((lane >> 2) & 7), tot);
+                    if (live_b) {
+                        float rpart[8];
+#pragma unroll
+                        for (int r = 0; r < 8; r++)
+                            rpart[r] = fmaf(e[r].w, b4.w, fmaf(e[r].z, b4.z, fmaf(e[r].y, b4.y, e[r].x * b4.x)));
+                        const float tot = reduce8_transposed(rpart, lane);
+                        if ((lane & 3) == 0) atomicAdd(sb + i0 + ((lane >> 2) & 7), tot);
+                    }
                 }
             }
             atomicAdd(sa + col, acc0);
@@ -327,12 +349,14 @@ dag_fast_sweep_kernel(const float *__restrict__ match_all, const float *__restri
         // ---- finalisation: every accumulator touched this step is consumed and cleared
         const float sca = pow2i(-sha), scb = pow2i(-shb);
         float vmax_a = 0.f, vmax_b = 0.f, vmax_bb = 0.f;
-        for (int j = 128 * cb_lo + tid; j < 128 * (cb_hi + 1); j += kFastThreads) {
+        int fq = 0;
+        for (int j = 128 * cb_lo + tid; j < 128 * (cb_hi + 1); j += kFastThreads, fq++) {
             const float s = sa[j];
             sa[j] = 0.f;
             const int c = j - ta;
             if (c >= 0 && c < W) {
-                const float m2 = __ldg(match + (size_t)ta * L + j) * kLog2e;
+                const float mt = fq == 0 ? mpa[0] : (fq == 1 ? mpa[1] : __ldg(match + (size_t)ta * L + j));
+                const float m2 = mt * kLog2e;
                 tiny |= (m2 < kMinLog2Input) && (m2 > -INFINITY);
                 const float pm = ex2(m2);
                 const float a = (s * sca) * pm;
@@ -341,12 +365,14 @@ dag_fast_sweep_kernel(const float *__restrict__ match_all, const float *__restri
                 vmax_a = fmaxf(vmax_a, a);
             }
         }
-        for (int i = 16 * rt_lo + tid; i < 16 * (rt_hi + 1); i += kFastThreads) {
+        fq = 0;
+        for (int i = 16 * rt_lo + tid; i < 16 * (rt_hi + 1); i += kFastThreads, fq++) {
             const float s = sb[i];
             sb[i] = 0.f;
             const int r = i - tb;
             if (r >= 0 && r < W) {
-                const float m2 = __ldg(match + (size_t)tb * L + i) * kLog2e;
+                const float mt = fq == 0 ? mpb[0] : (fq == 1 ? mpb[1] : __ldg(match + (size_t)tb * L + i));
+                const float m2 = mt * kLog2e;
                 tiny |= (m2 < kMinLog2Input) && (m2 > -INFINITY);
                 const float pm = ex2(m2);
                 const float bv = (s * scb) * pm;
