@@ -156,6 +156,43 @@ def cpu_baseline(budget_s=12.0):
                       f"(oracle/dag_oracle.c, OpenMP over sentences): best alignment + alpha + beta + backward"}
 
 
+def reference_cuda_baseline(match, links, ol, tl, gout, iters=5):
+    """GPU baseline leg: the same step on the REFERENCE's own CUDA kernels (compiled unmodified
+    by oracle/build_ref.py, default launch configs), when that build is present.  A baseline
+    printed next to our numbers, never part of the measured path."""
+    import torch
+
+    from oracle import ref_cuda
+
+    if not ref_cuda.available():
+        return {"unavailable": "oracle/_ref/dag_loss_fn.so not built"}
+    B = match.shape[0]
+    m, l = match.detach(), links.detach()
+    g = gout.contiguous()
+
+    def step():
+        ref_cuda.dag_best_alignment(m, l, ol, tl)
+        ref_cuda.dag_loss_fwd_bwd(m, l, ol, tl, g)
+
+    def timed(fn, n):
+        fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+
+    ms = timed(step, iters)
+    ms_align = timed(lambda: ref_cuda.dag_best_alignment(m, l, ol, tl), iters)
+    return {"value": B / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "best_alignment_ms": ms_align,
+            "dag_loss_fwd_bwd_ms": ms - ms_align,
+            "what": "reference CUDA extension (dag_loss.cu, dag_best_alignment.cu) built for sm_100, "
+                    "default configs, same 512-sentence shard, same step"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -431,6 +468,7 @@ def main():
                                   "peak_kind": peak_kind}
     if world == 1 and not args.no_cpu_baseline:
         out["cpu_baseline"] = cpu_baseline()
+        out["reference_cuda"] = reference_cuda_baseline(match, links, ol, tl, gout)
     print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
