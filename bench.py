@@ -360,25 +360,51 @@ def main():
     d2h = 4 * 8
     stats_host = torch.empty(4, dtype=torch.float64).pin_memory()
 
-    def e2e_step():
-        m = host[0].to(dev, non_blocking=True).requires_grad_()
-        l = host[1].to(dev, non_blocking=True).requires_grad_()
-        o = host[2].to(dev, non_blocking=True)
-        t = host[3].to(dev, non_blocking=True)
+    # The copies of step i+1 run on a second stream while step i computes (two device buffer sets),
+    # the way an input pipeline feeds a training step; every step still pays its own full
+    # host-to-device copy and its own device-to-host read of the statistics.
+    copy_stream = torch.cuda.Stream(device=dev)
+    bufs = [[torch.empty_like(h, device=dev) for h in host] for _ in range(2)]
+    ready = [torch.cuda.Event() for _ in range(2)]
+    freed = [torch.cuda.Event() for _ in range(2)]
+
+    def e2e_upload(slot):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(freed[slot])          # the step that used this slot is done
+            for d, h in zip(bufs[slot], host):
+                d.copy_(h, non_blocking=True)
+            ready[slot].record(copy_stream)
+
+    def e2e_compute(slot):
+        cur = torch.cuda.current_stream()
+        cur.wait_event(ready[slot])
+        m = bufs[slot][0].requires_grad_()
+        l = bufs[slot][1].requires_grad_()
+        o, t = bufs[slot][2], bufs[slot][3]
         dag_best_alignment(m.detach(), l.detach(), o, t)
         loss = dag_loss(m, l, o, t)
         torch.autograd.grad(loss, [m, l], grad_outputs=gout)
         s = ddist.all_reduce_stats(ddist.sentence_stats(loss.detach(), t))
         stats_host.copy_(s, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        freed[slot].record(cur)
+        m.requires_grad_(False)
+        l.requires_grad_(False)
 
-    for _ in range(3):
-        e2e_step()
+    def e2e_run(n):
+        for f in freed:
+            f.record(torch.cuda.current_stream())
+        e2e_upload(0)
+        for i in range(n):
+            if i + 1 < n:
+                e2e_upload((i + 1) & 1)
+            e2e_compute(i & 1)
+        torch.cuda.current_stream().synchronize()      # the last statistics have reached the host
+
+    e2e_run(3)
     barrier()
     t0, t1 = ev(), ev()
     t0.record()
-    for _ in range(args.steps):
-        e2e_step()
+    e2e_run(args.steps)
     t1.record()
     barrier()
     e2e_ms = t0.elapsed_time(t1)
@@ -452,7 +478,10 @@ def main():
             "kernel": ("dag_loss forward = dag_fast_sweep_kernel (fused alpha+beta recursion) with its "
                        "exp(links) preparation, check and fallback launches"),
             "bound": "mufu", "achieved": sweep_rate / 1e9, "peak": mufu_peak / 1e9, "unit": "Gexp/s",
-            "frac": sweep_rate / mufu_peak, "traffic": None,
+            "frac": sweep_rate / mufu_peak,
+            # dram__bytes_read+write of dag_fast_sweep_kernel from the ncu capture summarised in
+            # profiles/dag_fast_sweep_c4_148sent.md (134.9 MB for 148 sentences), scaled by sentences
+            "traffic": 134.9e6 / 148 * B,
             "peak_kind": "measured on this device by dat_probe_mufu just before the timed region",
             "nominal_peak": 16 * sm_count * peaks.get("sm_max_mhz", 1965.0) * 1e6 / 1e9,
             "algorithmic_exps_per_launch": sweep_exps, "kernel_ms": sweep_ms,

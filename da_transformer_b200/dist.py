@@ -31,7 +31,7 @@ def sentence_stats(loss_result: torch.Tensor, target_length: torch.Tensor) -> to
     return torch.stack([
         (clean / tl).sum(),
         tl.sum(),
-        torch.tensor(float(loss_result.numel()), dtype=torch.float64, device=loss_result.device),
+        clean.new_full((), float(loss_result.numel())),   # a fill kernel: no host-to-device copy, no sync
         invalid.sum().to(torch.float64),
     ])
 
