@@ -16,4 +16,10 @@ from .dag_loss import (  # noqa: F401
     logsoftmax_gather,
 )
 
+from .torch_twins import (  # noqa: F401
+    torch_dag_best_alignment,
+    torch_dag_logsoftmax_gather_inplace,
+    torch_dag_loss,
+)
+
 __version__ = "0.1.0"
