@@ -393,3 +393,40 @@ def test_fast_path_hands_extreme_dynamic_range_to_the_exact_kernels(dag_loss_pat
     check_dag_against_oracle(batch)
     if dag_loss_path == "fast":
         assert last_status() & 8
+
+
+def test_c1_shaped_chain_with_fp16_logits(dag_loss_path):
+    """C1 shape (ragged lengths, L = 8 x source, V = 42000, fp16 logits), chained like the
+    criterion: gather -> alignment -> loss -> backward down to the logits.  Checked through
+    size-independent properties and, on a few rows, against the oracle."""
+    batch = workloads.config1(B=6).to(DEV)
+    B, L, V = batch.logits.shape
+    tl, ol = batch.target_length, batch.output_length
+    logits = batch.logits.clone().requires_grad_()
+    links = batch.links.clone().requires_grad_()
+    last_status()
+    _, sel = dag_logsoftmax_gather_inplace(logits.clone(), batch.select_idx)
+    match = sel.transpose(1, 2)
+    path = dag_best_alignment(match.detach(), links.detach(), ol, tl)
+    loss = dag_loss(match, links, ol, tl)
+    assert torch.isfinite(loss).all()
+    (-(loss / tl).mean()).backward()
+    assert last_status() == 0
+    # gather rows against the oracle
+    rows = [(0, 0), (1, 7), (B - 1, int(ol[B - 1]) - 1)]
+    for b, l in rows:
+        ref = oracle.logsoftmax_gather(batch.logits[b:b + 1, l:l + 1].float().cpu().numpy(),
+                                       batch.targets[b:b + 1].unsqueeze(1).cpu().numpy())
+        assert_rel(sel[b, l].detach().cpu().numpy()[None, None], ref, TOL_SEL, "sel row")
+    # the gradient of a log-softmax sums to zero over the vocabulary; padded rows get none
+    dl = logits.grad.float()
+    rowsum = dl.sum(-1).abs().max().item()
+    assert rowsum <= 2e-3 * dl.abs().max().item() * 8
+    for b in range(B):
+        assert (dl[b, int(ol[b]):] == 0).all()
+    # every aligned path is complete and monotone
+    p = path.cpu().numpy()
+    for b in range(B):
+        pos = np.nonzero(p[b] >= 0)[0]
+        assert p[b][pos].tolist() == list(range(int(tl[b]))) and pos[-1] == int(ol[b]) - 1
+    assert torch.isfinite(links.grad).all() and (links.grad <= 0).all()   # d(-loss)/d links <= 0
