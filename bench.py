@@ -66,24 +66,31 @@ def exp_counts(ol, tl, K):
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """Samples SM clock and throttle reasons with nvidia-smi.  It is started well before the
+    timed region (its start-up talks to the driver for tens of milliseconds and would stall
+    kernel launches if it overlapped the region); the samples whose timestamps fall inside the
+    region are the ones reported."""
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index):
-        self.gpu = gpu_index
+    def __init__(self, gpu_id):
+        self.gpu = gpu_id
         self.proc = None
         self.lines = []
+        self.t_begin = self.t_end = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            deadline = time.time() + 3.0
+            while not self.lines and time.time() < deadline:   # start-up is over once it prints
+                time.sleep(0.01)
         except OSError:
             self.proc = None
 
@@ -91,32 +98,44 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def begin(self):
+        self.t_begin = time.time()
+
+    def end(self):
+        self.t_end = time.time()
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        import datetime
+
+        rows = []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
                 continue
             try:
-                sm.append(float(parts[1]))
-                mx.append(float(parts[2]))
+                ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(parts[1]), float(parts[2]),
+                             [n for n, v in zip(names, parts[5:9]) if v.lower().startswith("active")]))
             except ValueError:
                 continue
-            for name, val in zip(names, parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
+        inside = [r for r in rows if self.t_begin is not None and self.t_begin - 0.02 <= r[0] <= self.t_end + 0.02]
+        where = "timed region"
+        if not inside:   # clock skew between nvidia-smi's timestamps and this process: use all samples
+            inside, where = rows, "whole run (no sample carried a timestamp inside the region)"
+        sm = [r[1] for r in inside]
+        reasons = sorted({x for r in inside for x in r[3]})
         return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "sm_max_mhz": max(r[2] for r in inside) if inside else None,
+                "samples": len(sm), "window": where, "reasons": reasons}
 
 
 # --------------------------------------------------------------------------------------
@@ -227,7 +246,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sentences", type=int, default=SENTENCES_PER_GPU, help="sentences per GPU")
@@ -305,20 +324,22 @@ def main():
     mufu_peak = blocks * 1024 * 8 * iters / (e0.elapsed_time(e1) * 1e-3)   # ex2 / s
 
     # ---- timed region: device-resident inputs
-    for _ in range(args.warmup):
-        step()
     uuid = str(torch.cuda.get_device_properties(dev).uuid)
     sampler = ClockSampler(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
-    marks = [(ev(), ev()) for _ in range(args.steps)]
-    barrier()
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        step()
+    marks = [(ev(), ev()) for _ in range(args.steps)]
+    barrier()
+    sampler.begin()
     t0, t1 = ev(), ev()
     t0.record()
     for k in range(args.steps):
         stats, _, _, _ = step(marks[k])
     t1.record()
     barrier()
+    sampler.end()
     clocks = sampler.stop() if rank == 0 else None
     elapsed_ms = t0.elapsed_time(t1)
     sweep_ms = sum(a.elapsed_time(b) for a, b in marks) / args.steps

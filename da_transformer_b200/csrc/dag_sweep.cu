@@ -86,7 +86,7 @@ __device__ void alpha_sweep(const float *__restrict__ match, const float *__rest
 #pragma unroll
         for (int q = 0; q < 2; q++) {
             int c = tid + q * kSweepThreads;
-            mt[q] = (c < W) ? __ldg(match + (size_t)t * L + t + c) : 0.f;
+            mt[q] = (c < W) ? ld_early(match + (size_t)t * L + t + c) : 0.f;
         }
         if (tid == 0) {
             const float *wm = sm.wmax + ((t - 1) & 1) * kSweepWarps;

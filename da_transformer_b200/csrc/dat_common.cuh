@@ -80,6 +80,14 @@ __device__ __forceinline__ uint4 ld_stream16(const void *p) {
     return v;
 }
 
+// A 4-byte read-only load the compiler will not move down to its first use: issued where it
+// is written, so that its latency overlaps the work in between.
+__device__ __forceinline__ float ld_early(const float *p) {
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+
 template <typename T>
 struct Elem;
 
