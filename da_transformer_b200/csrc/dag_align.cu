@@ -1,26 +1,28 @@
-// dag_best_alignment for sm_100a: max-plus (Viterbi) sweep with trace, and the backtrace,
-// in one launch.  Replaces calculate_maxalpha_kernel / calculate_backtrace_kernel and
-// their host wrapper (fs_plugins/custom_ops/dag_best_alignment.cu:39-130, 170-189,
-// 219-263) and the int32 -> int64 cast of fs_plugins/custom_ops/dag_loss.py:162.
+// dag_best_alignment for sm_100a: max-plus (Viterbi) sweep and the backtrace in one launch.
+// Replaces calculate_maxalpha_kernel / calculate_backtrace_kernel and their host wrapper
+// (fs_plugins/custom_ops/dag_best_alignment.cu:39-130, 170-189, 219-263) and the
+// int32 -> int64 cast of fs_plugins/custom_ops/dag_loss.py:162.
 //
 // Values are the reference's own fp32 sums (alpha[t-1,i] + links[i,d-1], then + match[t,j]),
-// so the maxima are bit-identical; the winner among equal candidates follows the
-// reference's lane scan + shfl_down tree for TRANS_BLOCK_SIZE = 2^lg lanes
-// (dag_best_alignment.cu:96-111): lane = (d-1) mod 2^lg, lanes preferred in bit-reversed
-// order, then the smaller distance d.  That order is a total order on (value, rank), so any
-// reduction tree gives the reference's answer.
+// so the maxima are bit-identical.  The reference records the winning predecessor of EVERY
+// (t, j) during the sweep; only the tl-1 entries on the best path are ever read.  Here the
+// sweep keeps just the row maxima (an add and a three-input max per two candidates) and keeps
+// all rows; the backtrace then recomputes, for the one vertex per step that lies on the path,
+// the candidates alpha[t-1,i] + links[i,pos] (the same fp32 additions, hence the same bits)
+// and picks the winner among the maximal ones with the reference's rule: its lane scan +
+// shfl_down tree for TRANS_BLOCK_SIZE = 2^lg lanes (dag_best_alignment.cu:96-111) prefers
+// lane = (d-1) mod 2^lg in bit-reversed order, then the smaller distance d.  That is a total
+// order on (value, rank), so one max-reduction over 64-bit keys gives the reference's answer.
 //
 // Layout: the band is first copied into a square, 16-byte aligned matrix Lsq[i][j] with
 // -inf everywhere a transition does not exist (dag_align_prep_kernel).  In absolute vertex
 // coordinates -inf replaces all masks (as 0 does in the probability-domain loss kernel), so
-// a warp reads tiles of 16 rows x 128 columns with aligned 128-bit loads and no predicates;
-// each lane owns 4 columns.  Per candidate the common path is 5 instructions (add, two
-// compares, max, select); a chunk in which any lane saw an exact tie is redone with the full
-// tie-break rule.  Warps merge their per-column winners through shared memory with a 64-bit
-// atomicMax on (order-preserving value bits, inverted rank).
+// a warp reads half-tiles of 8 rows x 128 columns with aligned 128-bit loads and no
+// predicates; each lane owns 4 columns.  Warps merge their per-column maxima through shared
+// memory with a 32-bit atomicMax on order-preserving value bits.
 //
-// One CTA owns one sentence; the trace (predecessor distances, uint16) stays in shared
-// memory when it fits, and one thread walks it back at the end of the same launch.
+// One CTA owns one sentence; the rows stay in shared memory when they fit (else in the
+// caller's workspace).
 #include "dag_tiles.cuh"
 
 namespace dat {
@@ -28,7 +30,6 @@ namespace dat {
 constexpr int kAlignThreads = 512;
 constexpr int kAlignWarps = kAlignThreads / 32;
 constexpr int kRankNone = 0x7fffffff;
-constexpr float kNoCand = -3.402823466e+38f;
 
 __host__ __device__ inline int align_pitch(int L) { return (L + 127) & ~127; }
 __host__ __device__ inline int align_rows(int L) { return (L + 15) & ~15; }
@@ -80,14 +81,30 @@ dag_align_prep_kernel(const float *__restrict__ links, const int64_t *__restrict
     }
 }
 
-template <bool kTraceInSmem>
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;  // three-input maximum of sm_100 (NaN operands are ignored, as by fmaxf)
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+__device__ __forceinline__ unsigned long long shfl_xor_u64(unsigned long long v, int m) {
+    const unsigned lo = __shfl_xor_sync(0xffffffffu, (unsigned)v, m);
+    const unsigned hi = __shfl_xor_sync(0xffffffffu, (unsigned)(v >> 32), m);
+    return ((unsigned long long)hi << 32) | lo;
+}
+
+// kRowsInSmem: all tl rows live in shared memory in absolute vertex coordinates (stride
+// pitch+32, -inf outside the reachable window).  Otherwise two row buffers ping-pong in shared
+// memory and every finished row is also written to rows_ws[b][t][j] for the backtrace.
+template <bool kRowsInSmem>
 __global__ void __launch_bounds__(kAlignThreads, 1)
 dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ lsq_all,
                  const int64_t *__restrict__ output_length, const int64_t *__restrict__ target_length,
                  int64_t *__restrict__ path_out, float *__restrict__ max_score,
-                 uint16_t *__restrict__ trace_ws, int32_t *__restrict__ status, int T, int L, int K,
+                 float *rows_ws, int32_t *__restrict__ status, int T, int L, int K,
                  int lg, int rows, int pitch) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ unsigned long long bt_key[3];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.x;
     int64_t *path = path_out + (size_t)b * L;
@@ -105,33 +122,36 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
     const float *match = match_all + (size_t)b * T * L;
     const float *Lsq = lsq_all + (size_t)b * rows * pitch;
     const int rp = pitch + 32;
-    unsigned long long *skey = reinterpret_cast<unsigned long long *>(smem_raw);  // [pitch]
-    float *rbuf0 = reinterpret_cast<float *>(skey + pitch), *rbuf1 = rbuf0 + rp;
-    // trace[t][c]: distance d of the chosen predecessor of window column c at step t (0 = none)
-    uint16_t *trace = kTraceInSmem ? reinterpret_cast<uint16_t *>(rbuf1 + rp) : trace_ws + (size_t)b * T * L;
-    const int tstride = kTraceInSmem ? W : L;
-    const unsigned long long key_none = pack_key(-INFINITY, kRankNone);
+    unsigned *skey = reinterpret_cast<unsigned *>(smem_raw);  // [pitch] per-column merge slots
+    float *rbuf = reinterpret_cast<float *>(skey + pitch);    // tl rows, or 2 when the rows go to rows_ws
+    float *grow = kRowsInSmem ? nullptr : rows_ws + (size_t)b * T * L;
+    const unsigned key_none = orderable(-INFINITY);
 
-    for (int x = tid; x < 2 * rp; x += kAlignThreads) rbuf0[x] = -INFINITY;
+    for (int x = tid; x < (kRowsInSmem ? tl : 2) * rp; x += kAlignThreads) rbuf[x] = -INFINITY;
     for (int x = tid; x < pitch; x += kAlignThreads) skey[x] = key_none;
+    if (tid < 3) bt_key[tid] = 0ull;
     __syncthreads();
-    if (tid == 0) rbuf0[0] = match[0];
+    if (tid == 0) {
+        rbuf[0] = match[0];
+        if (!kRowsInSmem) grow[0] = match[0];
+    }
     __syncthreads();
 
     const int ncbmax = pitch >> 7;
     for (int t = 1; t < tl; t++) {
-        const float *prev = ((t - 1) & 1) ? rbuf1 : rbuf0;  // absolute coordinates, -inf outside the window
-        float *cur = (t & 1) ? rbuf1 : rbuf0;
-        // live region: rows [t-1, t+W-2], columns [t, t+W-1]
-        const int rt_lo = (t - 1) >> 4, rt_hi = (t + W - 2) >> 4;
+        // absolute coordinates, -inf outside the window
+        const float *prev = rbuf + (size_t)(kRowsInSmem ? (t - 1) : ((t - 1) & 1)) * rp;
+        float *cur = rbuf + (size_t)(kRowsInSmem ? t : (t & 1)) * rp;
+        // live region: rows [t-1, t+W-2], columns [t, t+W-1]; work unit = 8 rows x 128 columns
+        const int u_lo = (t - 1) >> 3, u_hi = (t + W - 2) >> 3;
         const int cb_lo = t >> 7;
         int cb_hi = (t + W - 1) >> 7;
         if (cb_hi > ncbmax - 1) cb_hi = ncbmax - 1;
         int total = 0;
         for (int cb = cb_lo; cb <= cb_hi; cb++) {
-            int rf = 128 * cb - K; rf = rf > 0 ? (rf >> 4) : 0; rf = rf > rt_lo ? rf : rt_lo;
-            int rl = 8 * cb + 7; rl = rl < rt_hi ? rl : rt_hi;
-            total += rl >= rf ? rl - rf + 1 : 0;
+            int uf = 128 * cb - K; uf = uf > 0 ? (uf >> 3) : 0; uf = uf > u_lo ? uf : u_lo;
+            int ul = 16 * cb + 15; ul = ul < u_hi ? ul : u_hi;
+            total += ul >= uf ? ul - uf + 1 : 0;
         }
         const int my_lo = (warp * total) / kAlignWarps, my_hi = ((warp + 1) * total) / kAlignWarps;
         const bool reverse = t & 1;
@@ -145,124 +165,104 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
         int base = 0;
         for (int cbx = cb_lo; cbx <= cb_hi; cbx++) {
             const int cb = reverse ? (cb_hi - (cbx - cb_lo)) : cbx;
-            int rf = 128 * cb - K; rf = rf > 0 ? (rf >> 4) : 0; rf = rf > rt_lo ? rf : rt_lo;
-            int rl = 8 * cb + 7; rl = rl < rt_hi ? rl : rt_hi;
-            const int n = rl >= rf ? rl - rf + 1 : 0;
+            int uf = 128 * cb - K; uf = uf > 0 ? (uf >> 3) : 0; uf = uf > u_lo ? uf : u_lo;
+            int ul = 16 * cb + 15; ul = ul < u_hi ? ul : u_hi;
+            const int n = ul >= uf ? ul - uf + 1 : 0;
             const int from = my_lo > base ? my_lo - base : 0;
             const int to = my_hi < base + n ? my_hi - base : n;
             base += n;
             if (from >= to) continue;
             const int col = 128 * cb + 4 * lane;
-            // "nothing yet" is the most negative finite float rather than -inf, so that the
-            // -inf of non-existent transitions never compares equal to it (no false ties)
-            float bv[4] = {kNoCand, kNoCand, kNoCand, kNoCand};
-            int bi[4] = {-1, -1, -1, -1};
+            float bv[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 2
             for (int q = from; q < to; q++) {
-                const int rt = reverse ? (rl - q) : (rf + q);
+                const int i0 = 8 * (reverse ? (ul - q) : (uf + q));
+                const float4 *ep = reinterpret_cast<const float4 *>(Lsq + (size_t)i0 * pitch + col);
+                float4 e[8];
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const int i0 = 16 * rt + 8 * h;
-                    const float4 *ep = reinterpret_cast<const float4 *>(Lsq + (size_t)i0 * pitch + col);
-                    float4 e[8];
+                for (int r = 0; r < 8; r++) e[r] = __ldg(ep + (size_t)r * (pitch >> 2));
+                const float4 a0 = *reinterpret_cast<const float4 *>(prev + i0);
+                const float4 a1 = *reinterpret_cast<const float4 *>(prev + i0 + 4);
+                const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
 #pragma unroll
-                    for (int r = 0; r < 8; r++) e[r] = __ldg(ep + (size_t)r * (pitch >> 2));
-                    const float4 a0 = *reinterpret_cast<const float4 *>(prev + i0);
-                    const float4 a1 = *reinterpret_cast<const float4 *>(prev + i0 + 4);
-                    const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                    const float sv[4] = {bv[0], bv[1], bv[2], bv[3]};
-                    const int si[4] = {bi[0], bi[1], bi[2], bi[3]};
-                    bool tie = false;
-#pragma unroll
-                    for (int r = 0; r < 8; r++) {
-                        const float v[4] = {__fadd_rn(av[r], e[r].x), __fadd_rn(av[r], e[r].y),
-                                            __fadd_rn(av[r], e[r].z), __fadd_rn(av[r], e[r].w)};
-#pragma unroll
-                        for (int k = 0; k < 4; k++) {
-                            tie |= (v[k] == bv[k]);
-                            const bool up = v[k] > bv[k];
-                            bv[k] = up ? v[k] : bv[k];
-                            bi[k] = up ? (i0 + r) : bi[k];
-                        }
-                    }
-                    if (__any_sync(0xffffffffu, tie)) {
-                        // redo the chunk with the reference's full tie-break
-#pragma unroll
-                        for (int k = 0; k < 4; k++) { bv[k] = sv[k]; bi[k] = si[k]; }
-#pragma unroll
-                        for (int r = 0; r < 8; r++) {
-                            const float v[4] = {__fadd_rn(av[r], e[r].x), __fadd_rn(av[r], e[r].y),
-                                                __fadd_rn(av[r], e[r].z), __fadd_rn(av[r], e[r].w)};
-#pragma unroll
-                            for (int k = 0; k < 4; k++) {
-                                const int j = col + k, i = i0 + r;
-                                bool up = v[k] > bv[k];
-                                if (!up && v[k] == bv[k] && v[k] > -INFINITY && j > i) {
-                                    const int rnew = tie_rank(j - i, lg);
-                                    const int rold = bi[k] >= 0 ? tie_rank(j - bi[k], lg) : kRankNone;
-                                    up = rnew < rold;
-                                }
-                                if (up) { bv[k] = v[k]; bi[k] = i; }
-                            }
-                        }
-                    }
+                for (int r = 0; r < 8; r += 2) {
+                    bv[0] = max3(bv[0], __fadd_rn(av[r], e[r].x), __fadd_rn(av[r + 1], e[r + 1].x));
+                    bv[1] = max3(bv[1], __fadd_rn(av[r], e[r].y), __fadd_rn(av[r + 1], e[r + 1].y));
+                    bv[2] = max3(bv[2], __fadd_rn(av[r], e[r].z), __fadd_rn(av[r + 1], e[r + 1].z));
+                    bv[3] = max3(bv[3], __fadd_rn(av[r], e[r].w), __fadd_rn(av[r + 1], e[r + 1].w));
                 }
             }
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const int rank = (bi[k] >= 0) ? tie_rank(col + k - bi[k], lg) : kRankNone;
-                if (rank != kRankNone) atomicMax(skey + col + k, pack_key(bv[k], rank));
-            }
+            for (int k = 0; k < 4; k++)
+                if (bv[k] > -INFINITY) atomicMax(skey + col + k, orderable(bv[k]));
         }
         __syncthreads();
 
         // finalisation: consume and clear every merge slot that may have been touched
         int fq = 0;
         for (int j = 128 * cb_lo + tid; j < 128 * (cb_hi + 1); j += kAlignThreads, fq++) {
-            const unsigned long long key = skey[j];
+            const unsigned key = skey[j];
             skey[j] = key_none;
             const int c = j - t;
             if (c >= 0 && c < W) {
-                const float best = unorderable((unsigned)(key >> 32));
-                const int rank = (int)(0xffffffffu - (unsigned)(key & 0xffffffffu));
+                const float best = unorderable(key);
                 const float mt = fq == 0 ? mp[0] : (fq == 1 ? mp[1] : __ldg(match + (size_t)t * L + j));
                 float v = __fadd_rn(best, mt);
                 if (!(v > -INFINITY)) v = -INFINITY;
                 cur[j] = v;
-                const int d = (rank == kRankNone) ? 0 : (rank & 0xfffff);
-                trace[(size_t)t * tstride + (kTraceInSmem ? c : j)] = (uint16_t)d;
+                if (!kRowsInSmem) grow[(size_t)t * L + j] = v;
             }
         }
-        if (tid == 0) {  // entries of the recycled row buffer that left the window
+        if (!kRowsInSmem && tid == 0) {  // entries of the recycled row buffer that left the window
             cur[t - 1] = -INFINITY;
             if (t >= 2) cur[t - 2] = -INFINITY;
         }
         __syncthreads();
     }
 
-    // backtrace (dag_best_alignment.cu:185-188), one thread
-    if (tid == 0) {
-        const float score = (((tl - 1) & 1) ? rbuf1 : rbuf0)[ol - 1];
-        if (max_score) max_score[b] = score;
-        if (score > -INFINITY) {
-            int pos = ol - 1;
-            for (int t = tl - 1; t >= 0; t--) {
-                path[pos] = t;
-                if (t == 0) break;
-                const int c = pos - t;
-                if (c < 0 || c >= W) break;  // cannot happen on a finite path
-                const int d = trace[(size_t)t * tstride + (kTraceInSmem ? c : pos)];
-                if (d == 0 || d > pos) break;
-                pos -= d;
+    // backtrace (dag_best_alignment.cu:185-188).  At each step every thread re-evaluates one
+    // candidate predecessor of the path vertex; the CTA keeps the largest (value, rank) key.
+    const float score = rbuf[(size_t)(kRowsInSmem ? (tl - 1) : ((tl - 1) & 1)) * rp + (ol - 1)];
+    if (tid == 0 && max_score) max_score[b] = score;
+    if (!(score > -INFINITY)) {
+        if (tid == 0 && status) atomicOr(status, DAT_STATUS_NO_PATH);
+        return;
+    }
+    int pos = ol - 1;
+    if (tid == 0) path[pos] = tl - 1;
+    for (int t = tl - 1; t >= 1; t--) {
+        const int slot = t % 3;
+        int lo = pos - K; lo = lo > t - 1 ? lo : t - 1;
+        int hi = t + W - 2; hi = hi < pos - 1 ? hi : pos - 1;
+        unsigned long long key = 0ull;
+        for (int i = lo + tid; i <= hi; i += kAlignThreads) {
+            const float a = kRowsInSmem ? rbuf[(size_t)(t - 1) * rp + i] : grow[(size_t)(t - 1) * L + i];
+            const float v = __fadd_rn(a, __ldg(Lsq + (size_t)i * pitch + pos));
+            if (v > -INFINITY) {
+                const unsigned long long kk = pack_key(v, tie_rank(pos - i, lg));
+                key = kk > key ? kk : key;
             }
-        } else if (status) {
-            atomicOr(status, DAT_STATUS_NO_PATH);
         }
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) {
+            const unsigned long long o = shfl_xor_u64(key, m);
+            key = o > key ? o : key;
+        }
+        if (lane == 0 && key != 0ull) atomicMax(&bt_key[slot], key);
+        if (tid == 0) bt_key[(t + 2) % 3] = 0ull;   // the slot of the next step; last read two steps ago
+        __syncthreads();
+        const unsigned long long win = bt_key[slot];
+        if (win == 0ull) break;                      // cannot happen on a finite path
+        const int d = (int)((0xffffffffu - (unsigned)(win & 0xffffffffu)) & 0xfffffu);
+        if (d <= 0 || d > pos) break;
+        pos -= d;
+        if (tid == 0) path[pos] = t - 1;
     }
 }
 
-static inline size_t align_base_smem(int L) {
+static inline size_t align_smem_bytes(int L, int nrows) {
     const int pitch = align_pitch(L);
-    return (size_t)pitch * 8 + (size_t)2 * (pitch + 32) * 4;
+    return ((size_t)pitch * 4 + (size_t)nrows * (pitch + 32) * 4 + 15) & ~(size_t)15;
 }
 static inline size_t align_lsq_bytes(int B, int L) {
     return (((size_t)B * align_rows(L) * align_pitch(L) * sizeof(float)) + 255) & ~(size_t)255;
@@ -274,8 +274,8 @@ extern "C" {
 
 size_t dat_dag_best_alignment_workspace_bytes(int bsz, int tarlen, int prelen) {
     if (bsz <= 0 || tarlen <= 0 || prelen <= 0) return 0;
-    // square copy of the links + (only used when it does not fit in shared memory) the trace
-    return dat::align_lsq_bytes(bsz, prelen) + (size_t)bsz * tarlen * prelen * sizeof(uint16_t) + 512;
+    // square copy of the links + (only used when they do not fit in shared memory) the rows
+    return dat::align_lsq_bytes(bsz, prelen) + (size_t)bsz * tarlen * prelen * sizeof(float) + 512;
 }
 
 int dat_dag_best_alignment(const float *match_all, const float *links,
@@ -301,22 +301,22 @@ int dat_dag_best_alignment(const float *match_all, const float *links,
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uintptr_t wbase = (reinterpret_cast<uintptr_t>(workspace) + 255) & ~(uintptr_t)255;
     float *lsq = reinterpret_cast<float *>(wbase);
-    uint16_t *trace_ws = reinterpret_cast<uint16_t *>(wbase + align_lsq_bytes(bsz, prelen));
+    float *rows_ws = reinterpret_cast<float *>(wbase + align_lsq_bytes(bsz, prelen));
     {
         dim3 grid((rows + 7) / 8, bsz);
         dag_align_prep_kernel<<<grid, 256, 0, st>>>(links, output_length, target_length, lsq, tarlen,
                                                     prelen, translen, rows, pitch);
         if (int rc = check_launch("dat_dag_best_alignment(prep)")) return rc;
     }
-    const size_t base = (align_base_smem(prelen) + 15) & ~(size_t)15;
-    DAT_REQUIRE(base <= (size_t)di.max_smem_optin, DAT_ERR_UNSUPPORTED,
+    const size_t base = align_smem_bytes(prelen, 2);
+    DAT_REQUIRE(base + 64 <= (size_t)di.max_smem_optin, DAT_ERR_UNSUPPORTED,
                 "dat_dag_best_alignment: prelen=%d needs %zu bytes of shared memory", prelen, base);
-    const size_t with_trace = base + (size_t)tarlen * prelen * sizeof(uint16_t);
-    if (with_trace <= (size_t)di.max_smem_optin) {
+    const size_t with_rows = align_smem_bytes(prelen, tarlen);
+    if (with_rows + 64 <= (size_t)di.max_smem_optin) {  // 64: the kernel's static shared variables
         if (cudaFuncSetAttribute(dag_align_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)with_trace) != cudaSuccess)
+                                 (int)with_rows) != cudaSuccess)
             return check_launch("dat_dag_best_alignment(attr)");
-        dag_align_kernel<true><<<(unsigned)bsz, kAlignThreads, with_trace, st>>>(
+        dag_align_kernel<true><<<(unsigned)bsz, kAlignThreads, with_rows, st>>>(
             match_all, lsq, output_length, target_length, path, max_score, nullptr, status, tarlen,
             prelen, translen, lg, rows, pitch);
     } else {
@@ -324,7 +324,7 @@ int dat_dag_best_alignment(const float *match_all, const float *links,
                                  (int)base) != cudaSuccess)
             return check_launch("dat_dag_best_alignment(attr)");
         dag_align_kernel<false><<<(unsigned)bsz, kAlignThreads, base, st>>>(
-            match_all, lsq, output_length, target_length, path, max_score, trace_ws, status, tarlen,
+            match_all, lsq, output_length, target_length, path, max_score, rows_ws, status, tarlen,
             prelen, translen, lg, rows, pitch);
     }
     return check_launch("dat_dag_best_alignment");
