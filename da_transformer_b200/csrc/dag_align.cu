@@ -129,6 +129,8 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
 
     for (int x = tid; x < (kRowsInSmem ? tl : 2) * rp; x += kAlignThreads) rbuf[x] = -INFINITY;
     for (int x = tid; x < pitch; x += kAlignThreads) skey[x] = key_none;
+    if (!kRowsInSmem)   // row 0 of the workspace copy: only vertex 0 is reachable
+        for (int j = 1 + tid; j < W; j += kAlignThreads) grow[j] = -INFINITY;
     if (tid < 3) bt_key[tid] = 0ull;
     __syncthreads();
     if (tid == 0) {
@@ -260,6 +262,218 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Strip kernel.  The recursion only ever looks left (alpha[t][j] needs alpha[t-1][i], i < j), so the
+// columns can be finished strip by strip, every target step of a strip before the next strip.
+// A 32 x 32 block of the transition matrix is then used for ALL steps while it sits in the
+// registers of one warp (lane = column, 32 rows per lane), and every transition is read from
+// memory once per launch, straight from the band, instead of once per target step.
+//
+// For strip s (columns 32s..32s+31):
+//   * blocks above the diagonal block (rows of an earlier strip c < s) have no dependency inside
+//     the strip: for each step t a warp takes the maximum over the 32 rows of
+//     alpha[t-1][32c+r] + link[32c+r][j] (the row values come from shared memory as broadcast
+//     loads) and merges it into P[t][j] with a shared atomicMax.  These (block, step) items are
+//     dealt out to warps 1..15 in contiguous ranges.
+//   * the diagonal block depends on the strip's own previous step, so one warp (warp 0) walks
+//     t in order: alpha[t][j] = max(P[t][j], max_{i in strip, i<j} alpha[t-1][i] + link[i][j])
+//     + match[t][j].
+// While warp 0 walks strip s, warps 1..15 already do the items of strip s+1 whose rows lie in
+// strips < s; the items whose rows are strip s itself follow in a short stage of their own.
+// Two CTA barriers per strip instead of two per target step.
+// ---------------------------------------------------------------------------------------------
+constexpr int kStripBulkWarps = kAlignWarps - 1;
+
+__device__ __forceinline__ void cp_async4(float *smem_dst, const float *gsrc) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+// e[r] = link from vertex 32c+r to vertex 32s+lane (band entry d = j-i-1), -inf if it does not exist
+__device__ __forceinline__ void strip_load_block(float (&e)[32], const float *__restrict__ links, int c,
+                                                 int s, int lane, int K, int ol) {
+    const int j = 32 * s + lane;
+#pragma unroll
+    for (int r = 0; r < 32; r++) {
+        const int i = 32 * c + r, d = j - i - 1;
+        const bool ok = d >= 0 && d < K && j < ol;
+        e[r] = ok ? __ldg(links + (size_t)i * K + d) : -INFINITY;
+    }
+}
+
+// max over the 32 rows of a block of arow[r] + e[r]; arow is read as broadcast 16-byte loads
+__device__ __forceinline__ float strip_block_max(const float *arow, const float (&e)[32]) {
+    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+    for (int q = 0; q < 8; q += 2) {
+        const float4 a = *reinterpret_cast<const float4 *>(arow + 4 * q);
+        const float4 b = *reinterpret_cast<const float4 *>(arow + 4 * q + 4);
+        m0 = max3(m0, __fadd_rn(a.x, e[4 * q]), __fadd_rn(a.y, e[4 * q + 1]));
+        m1 = max3(m1, __fadd_rn(a.z, e[4 * q + 2]), __fadd_rn(a.w, e[4 * q + 3]));
+        m2 = max3(m2, __fadd_rn(b.x, e[4 * q + 4]), __fadd_rn(b.y, e[4 * q + 5]));
+        m3 = max3(m3, __fadd_rn(b.z, e[4 * q + 6]), __fadd_rn(b.w, e[4 * q + 7]));
+    }
+    return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+
+// Items (block c, step t) of strip s for c in [c_first, c_last]; bulk warp wb of kStripBulkWarps
+// takes a contiguous share and merges its maxima into Pbuf[t][lane].
+__device__ __forceinline__ void strip_bulk(const float *__restrict__ links, const float *A, unsigned *Pbuf,
+                                           int c_first, int c_last, int s, int wb, int lane, int K,
+                                           int ol, int tl, int W, int rp) {
+    int t0 = 32 * s - W + 1; t0 = t0 > 1 ? t0 : 1;
+    int t1 = 32 * s + 31; t1 = t1 < tl - 1 ? t1 : tl - 1;
+    int total = 0;
+    for (int c = c_first; c <= c_last; c++) {
+        int ta = 32 * c - W + 2; ta = ta > t0 ? ta : t0;
+        int tb = 32 * c + 32; tb = tb < t1 ? tb : t1;
+        total += tb >= ta ? tb - ta + 1 : 0;
+    }
+    const int lo = (wb * total) / kStripBulkWarps, hi = ((wb + 1) * total) / kStripBulkWarps;
+    int base = 0;
+    for (int c = c_first; c <= c_last; c++) {
+        int ta = 32 * c - W + 2; ta = ta > t0 ? ta : t0;
+        int tb = 32 * c + 32; tb = tb < t1 ? tb : t1;
+        const int n = tb >= ta ? tb - ta + 1 : 0;
+        const int from = lo > base ? lo - base : 0;
+        const int to = hi < base + n ? hi - base : n;
+        base += n;
+        if (from >= to) continue;
+        float e[32];
+        strip_load_block(e, links, c, s, lane, K, ol);
+        for (int q = from; q < to; q++) {
+            const int t = ta + q;
+            const float m = strip_block_max(A + (size_t)(t - 1) * rp + 32 * c, e);
+            if (m > -INFINITY) atomicMax(Pbuf + t * 32 + lane, orderable(m));
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kAlignThreads, 1)
+dag_align_strip_kernel(const float *__restrict__ match_all, const float *__restrict__ links_all,
+                       const int64_t *__restrict__ output_length, const int64_t *__restrict__ target_length,
+                       int64_t *__restrict__ path_out, float *__restrict__ max_score,
+                       int32_t *__restrict__ status, int T, int L, int K, int lg, int rp) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ unsigned long long bt_key[3];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int b = blockIdx.x;
+    int64_t *path = path_out + (size_t)b * L;
+    for (int j = tid; j < L; j += kAlignThreads) path[j] = -1;
+    const long long oll = output_length[b], tll = target_length[b];
+    if (!lengths_valid(oll, tll, T, L)) {
+        if (tid == 0) {
+            if (max_score) max_score[b] = -INFINITY;
+            if (status) atomicOr(status, DAT_STATUS_BAD_LENGTH);
+        }
+        return;
+    }
+    const int ol = (int)oll, tl = (int)tll;
+    const int W = ol - tl + 1;
+    const float *match = match_all + (size_t)b * T * L;
+    const float *links = links_all + (size_t)b * L * K;
+    float *A = reinterpret_cast<float *>(smem_raw);                    // [T][rp] rows, absolute columns
+    unsigned *P = reinterpret_cast<unsigned *>(A + (size_t)T * rp);    // [2][T][32] merged maxima of a strip
+    float *M = reinterpret_cast<float *>(P + 2 * T * 32);              // [2][T][32] match values of a strip
+    const unsigned key_none = orderable(-INFINITY);
+
+    for (int x = tid; x < tl * rp; x += kAlignThreads) A[x] = -INFINITY;
+    for (int x = tid; x < 2 * T * 32; x += kAlignThreads) P[x] = key_none;
+    for (int x = tid; x < tl * 32; x += kAlignThreads) {
+        const int t = x >> 5, jj = x & 31;
+        M[x] = jj < L ? match[(size_t)t * L + jj] : 0.f;
+    }
+    if (tid < 3) bt_key[tid] = 0ull;
+    __syncthreads();
+    if (tid == 0) A[0] = match[0];
+    __syncthreads();
+
+    const int ns = (ol + 31) >> 5;
+    for (int s = 0; s < ns; s++) {
+        unsigned *Pcur = P + (s & 1) * T * 32, *Pnext = P + ((s + 1) & 1) * T * 32;
+        const float *Mcur = M + (s & 1) * T * 32;
+        float *Mnext = M + ((s + 1) & 1) * T * 32;
+        // ---- stage A: the items of strip s whose rows are strip s-1 (finished just now)
+        for (int x = tid; x < tl * 32; x += kAlignThreads) Pnext[x] = key_none;
+        float ed[32];
+        if (warp == 0) {
+            strip_load_block(ed, links, s, s, lane, K, ol);   // diagonal block, in flight across the barrier
+        } else if (s >= 1) {
+            strip_bulk(links, A, Pcur, s - 1, s - 1, s, warp - 1, lane, K, ol, tl, W, rp);
+        }
+        __syncthreads();
+        // ---- stage B: warp 0 walks the diagonal block of strip s; the others work ahead on strip s+1
+        if (warp == 0) {
+            const int j = 32 * s + lane;
+            int t0 = 32 * s - W + 1; t0 = t0 > 1 ? t0 : 1;
+            int t1 = 32 * s + 31; t1 = t1 < tl - 1 ? t1 : tl - 1;
+            for (int t = t0; t <= t1; t++) {
+                float best = strip_block_max(A + (size_t)(t - 1) * rp + 32 * s, ed);
+                best = fmaxf(best, unorderable(Pcur[t * 32 + lane]));
+                float v = __fadd_rn(best, Mcur[t * 32 + lane]);
+                const bool valid = j >= t && j <= t + W - 1;
+                if (!(v > -INFINITY) || !valid) v = -INFINITY;
+                A[(size_t)t * rp + j] = v;
+                __syncwarp();
+            }
+        } else if (s + 1 < ns) {
+            for (int x = tid - 32; x < tl * 32; x += kAlignThreads - 32) {
+                const int t = x >> 5, jj = 32 * (s + 1) + (x & 31);
+                if (jj < L) cp_async4(Mnext + x, match + (size_t)t * L + jj);
+                else Mnext[x] = 0.f;
+            }
+            if (s >= 1) {
+                int cmin = s - (K - 1) / 32;   // blocks further left hold no transition into strip s+1
+                cmin = cmin > 0 ? cmin : 0;
+                strip_bulk(links, A, Pnext, cmin, s - 1, s + 1, warp - 1, lane, K, ol, tl, W, rp);
+            }
+            cp_async_wait_all();
+        }
+        __syncthreads();
+    }
+
+    // backtrace (dag_best_alignment.cu:185-188).  At each step every thread re-evaluates one
+    // candidate predecessor of the path vertex; the CTA keeps the largest (value, rank) key.
+    const float score = A[(size_t)(tl - 1) * rp + (ol - 1)];
+    if (tid == 0 && max_score) max_score[b] = score;
+    if (!(score > -INFINITY)) {
+        if (tid == 0 && status) atomicOr(status, DAT_STATUS_NO_PATH);
+        return;
+    }
+    int pos = ol - 1;
+    if (tid == 0) path[pos] = tl - 1;
+    for (int t = tl - 1; t >= 1; t--) {
+        const int slot = t % 3;
+        int lo = pos - K; lo = lo > t - 1 ? lo : t - 1;
+        int hi = t + W - 2; hi = hi < pos - 1 ? hi : pos - 1;
+        unsigned long long key = 0ull;
+        for (int i = lo + tid; i <= hi; i += kAlignThreads) {
+            const float v = __fadd_rn(A[(size_t)(t - 1) * rp + i], __ldg(links + (size_t)i * K + (pos - i - 1)));
+            if (v > -INFINITY) {
+                const unsigned long long kk = pack_key(v, tie_rank(pos - i, lg));
+                key = kk > key ? kk : key;
+            }
+        }
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) {
+            const unsigned long long o = shfl_xor_u64(key, m);
+            key = o > key ? o : key;
+        }
+        if (lane == 0 && key != 0ull) atomicMax(&bt_key[slot], key);
+        if (tid == 0) bt_key[(t + 2) % 3] = 0ull;   // the slot of the next step; last read two steps ago
+        __syncthreads();
+        const unsigned long long win = bt_key[slot];
+        if (win == 0ull) break;                      // cannot happen on a finite path
+        const int d = (int)((0xffffffffu - (unsigned)(win & 0xffffffffu)) & 0xfffffu);
+        if (d <= 0 || d > pos) break;
+        pos -= d;
+        if (tid == 0) path[pos] = t - 1;
+    }
+}
+
 static inline size_t align_smem_bytes(int L, int nrows) {
     const int pitch = align_pitch(L);
     return ((size_t)pitch * 4 + (size_t)nrows * (pitch + 32) * 4 + 15) & ~(size_t)15;
@@ -302,6 +516,20 @@ int dat_dag_best_alignment(const float *match_all, const float *links,
     const uintptr_t wbase = (reinterpret_cast<uintptr_t>(workspace) + 255) & ~(uintptr_t)255;
     float *lsq = reinterpret_cast<float *>(wbase);
     float *rows_ws = reinterpret_cast<float *>(wbase + align_lsq_bytes(bsz, prelen));
+    {
+        // strip kernel: all rows plus the per-strip staging must fit in shared memory
+        const int rp = (prelen + 31) & ~31;
+        const size_t strip_smem = ((size_t)tarlen * rp + (size_t)4 * tarlen * 32) * sizeof(float);
+        if (strip_smem + 64 <= (size_t)di.max_smem_optin) {
+            if (cudaFuncSetAttribute(dag_align_strip_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)strip_smem) != cudaSuccess)
+                return check_launch("dat_dag_best_alignment(attr)");
+            dag_align_strip_kernel<<<(unsigned)bsz, kAlignThreads, strip_smem, st>>>(
+                match_all, links, output_length, target_length, path, max_score, status, tarlen, prelen,
+                translen, lg, rp);
+            return check_launch("dat_dag_best_alignment");
+        }
+    }
     {
         dim3 grid((rows + 7) / 8, bsz);
         dag_align_prep_kernel<<<grid, 256, 0, st>>>(links, output_length, target_length, lsq, tarlen,
