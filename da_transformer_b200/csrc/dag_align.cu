@@ -87,10 +87,22 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
-__device__ __forceinline__ unsigned long long shfl_xor_u64(unsigned long long v, int m) {
-    const unsigned lo = __shfl_xor_sync(0xffffffffu, (unsigned)v, m);
-    const unsigned hi = __shfl_xor_sync(0xffffffffu, (unsigned)(v >> 32), m);
-    return ((unsigned long long)hi << 32) | lo;
+// Largest 64-bit key over the CTA, returned to every thread: hardware warp reductions on the
+// two halves, one slot per warp, one CTA barrier.  `slots` alternates between two arrays from
+// one call to the next, so a slot is rewritten only after every thread has passed the barrier
+// that follows its last read.
+__device__ __forceinline__ unsigned long long cta_max_key(unsigned long long key, unsigned long long *slots,
+                                                          int lane, int warp) {
+    const unsigned hi = (unsigned)(key >> 32);
+    const unsigned mh = __reduce_max_sync(0xffffffffu, hi);
+    const unsigned ml = __reduce_max_sync(0xffffffffu, hi == mh ? (unsigned)key : 0u);
+    if (lane == 0) slots[warp] = ((unsigned long long)mh << 32) | ml;
+    __syncthreads();
+    const unsigned long long k = lane < kAlignWarps ? slots[lane] : 0ull;
+    const unsigned kh = (unsigned)(k >> 32);
+    const unsigned wh = __reduce_max_sync(0xffffffffu, kh);
+    const unsigned wl = __reduce_max_sync(0xffffffffu, kh == wh ? (unsigned)k : 0u);
+    return ((unsigned long long)wh << 32) | wl;
 }
 
 // kRowsInSmem: all tl rows live in shared memory in absolute vertex coordinates (stride
@@ -104,7 +116,7 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
                  float *rows_ws, int32_t *__restrict__ status, int T, int L, int K,
                  int lg, int rows, int pitch) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __shared__ unsigned long long bt_key[3];
+    __shared__ unsigned long long bt_key[2][kAlignWarps];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.x;
     int64_t *path = path_out + (size_t)b * L;
@@ -131,7 +143,6 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
     for (int x = tid; x < pitch; x += kAlignThreads) skey[x] = key_none;
     if (!kRowsInSmem)   // row 0 of the workspace copy: only vertex 0 is reachable
         for (int j = 1 + tid; j < W; j += kAlignThreads) grow[j] = -INFINITY;
-    if (tid < 3) bt_key[tid] = 0ull;
     __syncthreads();
     if (tid == 0) {
         rbuf[0] = match[0];
@@ -233,7 +244,6 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
     int pos = ol - 1;
     if (tid == 0) path[pos] = tl - 1;
     for (int t = tl - 1; t >= 1; t--) {
-        const int slot = t % 3;
         int lo = pos - K; lo = lo > t - 1 ? lo : t - 1;
         int hi = t + W - 2; hi = hi < pos - 1 ? hi : pos - 1;
         unsigned long long key = 0ull;
@@ -245,15 +255,7 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
                 key = kk > key ? kk : key;
             }
         }
-#pragma unroll
-        for (int m = 16; m >= 1; m >>= 1) {
-            const unsigned long long o = shfl_xor_u64(key, m);
-            key = o > key ? o : key;
-        }
-        if (lane == 0 && key != 0ull) atomicMax(&bt_key[slot], key);
-        if (tid == 0) bt_key[(t + 2) % 3] = 0ull;   // the slot of the next step; last read two steps ago
-        __syncthreads();
-        const unsigned long long win = bt_key[slot];
+        const unsigned long long win = cta_max_key(key, bt_key[t & 1], lane, warp);
         if (win == 0ull) break;                      // cannot happen on a finite path
         const int d = (int)((0xffffffffu - (unsigned)(win & 0xffffffffu)) & 0xfffffu);
         if (d <= 0 || d > pos) break;
@@ -269,20 +271,24 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
 // registers of one warp (lane = column, 32 rows per lane), and every transition is read from
 // memory once per launch, straight from the band, instead of once per target step.
 //
-// For strip s (columns 32s..32s+31):
-//   * blocks above the diagonal block (rows of an earlier strip c < s) have no dependency inside
-//     the strip: for each step t a warp takes the maximum over the 32 rows of
-//     alpha[t-1][32c+r] + link[32c+r][j] (the row values come from shared memory as broadcast
-//     loads) and merges it into P[t][j] with a shared atomicMax.  These (block, step) items are
-//     dealt out to warps 1..15 in contiguous ranges.
-//   * the diagonal block depends on the strip's own previous step, so one warp (warp 0) walks
-//     t in order: alpha[t][j] = max(P[t][j], max_{i in strip, i<j} alpha[t-1][i] + link[i][j])
-//     + match[t][j].
-// While warp 0 walks strip s, warps 1..15 already do the items of strip s+1 whose rows lie in
-// strips < s; the items whose rows are strip s itself follow in a short stage of their own.
+// Strips are 64 columns wide (two 32-column halves).  For strip S:
+//   * blocks whose rows belong to an earlier strip have no dependency inside the strip: an item
+//     (32 rows c, strip S, step t) is the maximum over the rows of alpha[t-1][32c+r] + link, for
+//     both halves at once (64 registers of links per lane; the 32 row values come from shared
+//     memory as broadcast loads, which is what bounds this kernel, so each loaded value feeds two
+//     additions).  Items are dealt out to the 13 bulk warps in contiguous ranges and merged into
+//     P[t][column] with a shared atomicMax.
+//   * the three blocks on the diagonal depend on the strip's own previous step and are walked in
+//     step order by three warps in a software pipeline, one named barrier per step:
+//     warp 0 the triangular block of the left half (step t), warp 2 the square block from the
+//     left half's rows to the right half's columns (step t, needs the left half at t-1), warp 1
+//     the triangular block of the right half (step t-1, needs the square block at t-1).
+// While the diagonal of strip S is walked, the bulk warps already do the items of strip S+1 whose
+// rows lie in strips < S; the items whose rows are strip S follow in a short stage of their own.
 // Two CTA barriers per strip instead of two per target step.
 // ---------------------------------------------------------------------------------------------
-constexpr int kStripBulkWarps = kAlignWarps - 1;
+constexpr int kStripDiagWarps = 3;
+constexpr int kStripBulkWarps = kAlignWarps - kStripDiagWarps;
 
 __device__ __forceinline__ void cp_async4(float *smem_dst, const float *gsrc) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -291,11 +297,15 @@ __device__ __forceinline__ void cp_async4(float *smem_dst, const float *gsrc) {
 __device__ __forceinline__ void cp_async_wait_all() {
     asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
+// barrier among the three diagonal warps only (also orders their shared-memory accesses)
+__device__ __forceinline__ void diag_group_sync() {
+    asm volatile("bar.sync 1, %0;" ::"n"(kStripDiagWarps * 32) : "memory");
+}
 
-// e[r] = link from vertex 32c+r to vertex 32s+lane (band entry d = j-i-1), -inf if it does not exist
+// e[r] = link from vertex 32c+r to vertex 32h+lane (band entry d = j-i-1), -inf if it does not exist
 __device__ __forceinline__ void strip_load_block(float (&e)[32], const float *__restrict__ links, int c,
-                                                 int s, int lane, int K, int ol) {
-    const int j = 32 * s + lane;
+                                                 int h, int lane, int K, int ol) {
+    const int j = 32 * h + lane;
 #pragma unroll
     for (int r = 0; r < 32; r++) {
         const int i = 32 * c + r, d = j - i - 1;
@@ -319,13 +329,29 @@ __device__ __forceinline__ float strip_block_max(const float *arow, const float 
     return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
 
-// Items (block c, step t) of strip s for c in [c_first, c_last]; bulk warp wb of kStripBulkWarps
-// takes a contiguous share and merges its maxima into Pbuf[t][lane].
+// the same for two blocks that share their rows (the two halves of a strip)
+__device__ __forceinline__ void strip_block_max2(const float *arow, const float (&e0)[32],
+                                                 const float (&e1)[32], float &r0, float &r1) {
+    float m0 = -INFINITY, m1 = -INFINITY, n0 = -INFINITY, n1 = -INFINITY;
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+        const float4 a = *reinterpret_cast<const float4 *>(arow + 4 * q);
+        m0 = max3(m0, __fadd_rn(a.x, e0[4 * q]), __fadd_rn(a.y, e0[4 * q + 1]));
+        m1 = max3(m1, __fadd_rn(a.z, e0[4 * q + 2]), __fadd_rn(a.w, e0[4 * q + 3]));
+        n0 = max3(n0, __fadd_rn(a.x, e1[4 * q]), __fadd_rn(a.y, e1[4 * q + 1]));
+        n1 = max3(n1, __fadd_rn(a.z, e1[4 * q + 2]), __fadd_rn(a.w, e1[4 * q + 3]));
+    }
+    r0 = fmaxf(m0, m1);
+    r1 = fmaxf(n0, n1);
+}
+
+// Items (32-row block c, step t) of strip S for c in [c_first, c_last]; bulk warp wb takes a
+// contiguous share and merges its maxima into Pbuf[t][0..63].
 __device__ __forceinline__ void strip_bulk(const float *__restrict__ links, const float *A, unsigned *Pbuf,
-                                           int c_first, int c_last, int s, int wb, int lane, int K,
+                                           int c_first, int c_last, int S, int wb, int lane, int K,
                                            int ol, int tl, int W, int rp) {
-    int t0 = 32 * s - W + 1; t0 = t0 > 1 ? t0 : 1;
-    int t1 = 32 * s + 31; t1 = t1 < tl - 1 ? t1 : tl - 1;
+    int t0 = 64 * S - W + 1; t0 = t0 > 1 ? t0 : 1;
+    int t1 = 64 * S + 63; t1 = t1 < tl - 1 ? t1 : tl - 1;
     int total = 0;
     for (int c = c_first; c <= c_last; c++) {
         int ta = 32 * c - W + 2; ta = ta > t0 ? ta : t0;
@@ -342,12 +368,16 @@ __device__ __forceinline__ void strip_bulk(const float *__restrict__ links, cons
         const int to = hi < base + n ? hi - base : n;
         base += n;
         if (from >= to) continue;
-        float e[32];
-        strip_load_block(e, links, c, s, lane, K, ol);
+        float e0[32], e1[32];
+        strip_load_block(e0, links, c, 2 * S, lane, K, ol);
+        strip_load_block(e1, links, c, 2 * S + 1, lane, K, ol);
+#pragma unroll 2
         for (int q = from; q < to; q++) {
             const int t = ta + q;
-            const float m = strip_block_max(A + (size_t)(t - 1) * rp + 32 * c, e);
-            if (m > -INFINITY) atomicMax(Pbuf + t * 32 + lane, orderable(m));
+            float m0, m1;
+            strip_block_max2(A + (size_t)(t - 1) * rp + 32 * c, e0, e1, m0, m1);
+            if (m0 > -INFINITY) atomicMax(Pbuf + t * 64 + lane, orderable(m0));
+            if (m1 > -INFINITY) atomicMax(Pbuf + t * 64 + 32 + lane, orderable(m1));
         }
     }
 }
@@ -358,7 +388,7 @@ dag_align_strip_kernel(const float *__restrict__ match_all, const float *__restr
                        int64_t *__restrict__ path_out, float *__restrict__ max_score,
                        int32_t *__restrict__ status, int T, int L, int K, int lg, int rp) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __shared__ unsigned long long bt_key[3];
+    __shared__ unsigned long long bt_key[2][kAlignWarps];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.x;
     int64_t *path = path_out + (size_t)b * L;
@@ -376,59 +406,72 @@ dag_align_strip_kernel(const float *__restrict__ match_all, const float *__restr
     const float *match = match_all + (size_t)b * T * L;
     const float *links = links_all + (size_t)b * L * K;
     float *A = reinterpret_cast<float *>(smem_raw);                    // [T][rp] rows, absolute columns
-    unsigned *P = reinterpret_cast<unsigned *>(A + (size_t)T * rp);    // [2][T][32] merged maxima of a strip
-    float *M = reinterpret_cast<float *>(P + 2 * T * 32);              // [2][T][32] match values of a strip
+    unsigned *P = reinterpret_cast<unsigned *>(A + (size_t)T * rp);    // [2][T][64] merged maxima of a strip
+    float *M = reinterpret_cast<float *>(P + 2 * T * 64);              // [2][T][64] match values of a strip
     const unsigned key_none = orderable(-INFINITY);
 
     for (int x = tid; x < tl * rp; x += kAlignThreads) A[x] = -INFINITY;
-    for (int x = tid; x < 2 * T * 32; x += kAlignThreads) P[x] = key_none;
-    for (int x = tid; x < tl * 32; x += kAlignThreads) {
-        const int t = x >> 5, jj = x & 31;
+    for (int x = tid; x < 2 * T * 64; x += kAlignThreads) P[x] = key_none;
+    for (int x = tid; x < tl * 64; x += kAlignThreads) {
+        const int t = x >> 6, jj = x & 63;
         M[x] = jj < L ? match[(size_t)t * L + jj] : 0.f;
     }
-    if (tid < 3) bt_key[tid] = 0ull;
     __syncthreads();
     if (tid == 0) A[0] = match[0];
     __syncthreads();
 
-    const int ns = (ol + 31) >> 5;
-    for (int s = 0; s < ns; s++) {
-        unsigned *Pcur = P + (s & 1) * T * 32, *Pnext = P + ((s + 1) & 1) * T * 32;
-        const float *Mcur = M + (s & 1) * T * 32;
-        float *Mnext = M + ((s + 1) & 1) * T * 32;
-        // ---- stage A: the items of strip s whose rows are strip s-1 (finished just now)
-        for (int x = tid; x < tl * 32; x += kAlignThreads) Pnext[x] = key_none;
-        float ed[32];
-        if (warp == 0) {
-            strip_load_block(ed, links, s, s, lane, K, ol);   // diagonal block, in flight across the barrier
-        } else if (s >= 1) {
-            strip_bulk(links, A, Pcur, s - 1, s - 1, s, warp - 1, lane, K, ol, tl, W, rp);
-        }
+    const int nS = (ol + 63) >> 6;
+    for (int S = 0; S < nS; S++) {
+        unsigned *Pcur = P + (S & 1) * T * 64, *Pnext = P + ((S + 1) & 1) * T * 64;
+        const float *Mcur = M + (S & 1) * T * 64;
+        float *Mnext = M + ((S + 1) & 1) * T * 64;
+        // ---- stage A: the items of strip S whose rows are strip S-1 (finished just now)
+        for (int x = tid; x < tl * 64; x += kAlignThreads) Pnext[x] = key_none;
+        float ed[32];   // diagonal warps: their block, in flight across the barrier
+        if (warp == 0) strip_load_block(ed, links, 2 * S, 2 * S, lane, K, ol);
+        else if (warp == 1) strip_load_block(ed, links, 2 * S + 1, 2 * S + 1, lane, K, ol);
+        else if (warp == 2) strip_load_block(ed, links, 2 * S, 2 * S + 1, lane, K, ol);
+        else if (S >= 1)
+            strip_bulk(links, A, Pcur, 2 * S - 2, 2 * S - 1, S, warp - kStripDiagWarps, lane, K, ol, tl, W, rp);
         __syncthreads();
-        // ---- stage B: warp 0 walks the diagonal block of strip s; the others work ahead on strip s+1
-        if (warp == 0) {
-            const int j = 32 * s + lane;
-            int t0 = 32 * s - W + 1; t0 = t0 > 1 ? t0 : 1;
-            int t1 = 32 * s + 31; t1 = t1 < tl - 1 ? t1 : tl - 1;
-            for (int t = t0; t <= t1; t++) {
-                float best = strip_block_max(A + (size_t)(t - 1) * rp + 32 * s, ed);
-                best = fmaxf(best, unorderable(Pcur[t * 32 + lane]));
-                float v = __fadd_rn(best, Mcur[t * 32 + lane]);
-                const bool valid = j >= t && j <= t + W - 1;
-                if (!(v > -INFINITY) || !valid) v = -INFINITY;
-                A[(size_t)t * rp + j] = v;
-                __syncwarp();
+        // ---- stage B: warps 0-2 walk the diagonal blocks of strip S; the others work ahead on strip S+1
+        if (warp < kStripDiagWarps) {
+            int t0 = 64 * S - W + 1; t0 = t0 > 1 ? t0 : 1;
+            int t1 = 64 * S + 63; t1 = t1 < tl - 1 ? t1 : tl - 1;
+            for (int tau = t0; tau <= t1 + 1; tau++) {
+                if (warp == 0 && tau <= t1) {
+                    const int t = tau, j = 64 * S + lane;
+                    float best = strip_block_max(A + (size_t)(t - 1) * rp + 64 * S, ed);
+                    best = fmaxf(best, unorderable(Pcur[t * 64 + lane]));
+                    float v = __fadd_rn(best, Mcur[t * 64 + lane]);
+                    if (!(v > -INFINITY) || j < t || j > t + W - 1) v = -INFINITY;
+                    A[(size_t)t * rp + j] = v;
+                } else if (warp == 2 && tau <= t1) {
+                    const int t = tau;
+                    const float m = strip_block_max(A + (size_t)(t - 1) * rp + 64 * S, ed);
+                    // the bulk contributions to this strip are complete; only this warp writes here now
+                    const unsigned o = orderable(m), p = Pcur[t * 64 + 32 + lane];
+                    if (m > -INFINITY && o > p) Pcur[t * 64 + 32 + lane] = o;
+                } else if (warp == 1 && tau > t0) {
+                    const int t = tau - 1, j = 64 * S + 32 + lane;
+                    float best = strip_block_max(A + (size_t)(t - 1) * rp + 64 * S + 32, ed);
+                    best = fmaxf(best, unorderable(Pcur[t * 64 + 32 + lane]));
+                    float v = __fadd_rn(best, Mcur[t * 64 + 32 + lane]);
+                    if (!(v > -INFINITY) || j < t || j > t + W - 1) v = -INFINITY;
+                    A[(size_t)t * rp + j] = v;
+                }
+                diag_group_sync();
             }
-        } else if (s + 1 < ns) {
-            for (int x = tid - 32; x < tl * 32; x += kAlignThreads - 32) {
-                const int t = x >> 5, jj = 32 * (s + 1) + (x & 31);
+        } else if (S + 1 < nS) {
+            for (int x = tid - 32 * kStripDiagWarps; x < tl * 64; x += kAlignThreads - 32 * kStripDiagWarps) {
+                const int t = x >> 6, jj = 64 * (S + 1) + (x & 63);
                 if (jj < L) cp_async4(Mnext + x, match + (size_t)t * L + jj);
                 else Mnext[x] = 0.f;
             }
-            if (s >= 1) {
-                int cmin = s - (K - 1) / 32;   // blocks further left hold no transition into strip s+1
+            if (S >= 1) {
+                int cmin = 2 * S + 1 - (K - 1) / 32;   // blocks further left hold no transition into strip S+1
                 cmin = cmin > 0 ? cmin : 0;
-                strip_bulk(links, A, Pnext, cmin, s - 1, s + 1, warp - 1, lane, K, ol, tl, W, rp);
+                strip_bulk(links, A, Pnext, cmin, 2 * S - 1, S + 1, warp - kStripDiagWarps, lane, K, ol, tl, W, rp);
             }
             cp_async_wait_all();
         }
@@ -446,7 +489,6 @@ dag_align_strip_kernel(const float *__restrict__ match_all, const float *__restr
     int pos = ol - 1;
     if (tid == 0) path[pos] = tl - 1;
     for (int t = tl - 1; t >= 1; t--) {
-        const int slot = t % 3;
         int lo = pos - K; lo = lo > t - 1 ? lo : t - 1;
         int hi = t + W - 2; hi = hi < pos - 1 ? hi : pos - 1;
         unsigned long long key = 0ull;
@@ -457,15 +499,7 @@ dag_align_strip_kernel(const float *__restrict__ match_all, const float *__restr
                 key = kk > key ? kk : key;
             }
         }
-#pragma unroll
-        for (int m = 16; m >= 1; m >>= 1) {
-            const unsigned long long o = shfl_xor_u64(key, m);
-            key = o > key ? o : key;
-        }
-        if (lane == 0 && key != 0ull) atomicMax(&bt_key[slot], key);
-        if (tid == 0) bt_key[(t + 2) % 3] = 0ull;   // the slot of the next step; last read two steps ago
-        __syncthreads();
-        const unsigned long long win = bt_key[slot];
+        const unsigned long long win = cta_max_key(key, bt_key[t & 1], lane, warp);
         if (win == 0ull) break;                      // cannot happen on a finite path
         const int d = (int)((0xffffffffu - (unsigned)(win & 0xffffffffu)) & 0xfffffu);
         if (d <= 0 || d > pos) break;
@@ -518,9 +552,9 @@ int dat_dag_best_alignment(const float *match_all, const float *links,
     float *rows_ws = reinterpret_cast<float *>(wbase + align_lsq_bytes(bsz, prelen));
     {
         // strip kernel: all rows plus the per-strip staging must fit in shared memory
-        const int rp = (prelen + 31) & ~31;
-        const size_t strip_smem = ((size_t)tarlen * rp + (size_t)4 * tarlen * 32) * sizeof(float);
-        if (strip_smem + 64 <= (size_t)di.max_smem_optin) {
+        const int rp = (prelen + 63) & ~63;
+        const size_t strip_smem = ((size_t)tarlen * rp + (size_t)4 * tarlen * 64) * sizeof(float);
+        if (strip_smem + 512 <= (size_t)di.max_smem_optin) {
             if (cudaFuncSetAttribute(dag_align_strip_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)strip_smem) != cudaSuccess)
                 return check_launch("dat_dag_best_alignment(attr)");
@@ -537,10 +571,10 @@ int dat_dag_best_alignment(const float *match_all, const float *links,
         if (int rc = check_launch("dat_dag_best_alignment(prep)")) return rc;
     }
     const size_t base = align_smem_bytes(prelen, 2);
-    DAT_REQUIRE(base + 64 <= (size_t)di.max_smem_optin, DAT_ERR_UNSUPPORTED,
+    DAT_REQUIRE(base + 512 <= (size_t)di.max_smem_optin, DAT_ERR_UNSUPPORTED,
                 "dat_dag_best_alignment: prelen=%d needs %zu bytes of shared memory", prelen, base);
     const size_t with_rows = align_smem_bytes(prelen, tarlen);
-    if (with_rows + 64 <= (size_t)di.max_smem_optin) {  // 64: the kernel's static shared variables
+    if (with_rows + 512 <= (size_t)di.max_smem_optin) {  // 512: room for the kernel's static shared variables
         if (cudaFuncSetAttribute(dag_align_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)with_rows) != cudaSuccess)
             return check_launch("dat_dag_best_alignment(attr)");
