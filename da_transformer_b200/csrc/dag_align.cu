@@ -302,15 +302,25 @@ __device__ __forceinline__ void diag_group_sync() {
     asm volatile("bar.sync 1, %0;" ::"n"(kStripDiagWarps * 32) : "memory");
 }
 
-// e[r] = link from vertex 32c+r to vertex 32h+lane (band entry d = j-i-1), -inf if it does not exist
+// e[r] = link from vertex 32c+r to vertex 32h+lane (band entry d = j-i-1), -inf if it does not exist.
+// Consecutive rows of one column lie K-1 floats apart in the band.  A block strictly left of the
+// diagonal whose every transition exists (the common case) is read without masks.
 __device__ __forceinline__ void strip_load_block(float (&e)[32], const float *__restrict__ links, int c,
                                                  int h, int lane, int K, int ol) {
     const int j = 32 * h + lane;
+    const int d0 = j - 32 * c - 1;                         // band index in row 32c
+    const bool full = h > c && 32 * (h - c) + 30 < K && 32 * h + 31 < ol;   // warp-uniform
+    if (full) {
+        const float *p = links + (size_t)(32 * c) * K + d0;
 #pragma unroll
-    for (int r = 0; r < 32; r++) {
-        const int i = 32 * c + r, d = j - i - 1;
-        const bool ok = d >= 0 && d < K && j < ol;
-        e[r] = ok ? __ldg(links + (size_t)i * K + d) : -INFINITY;
+        for (int r = 0; r < 32; r++) e[r] = __ldg(p + (size_t)r * (K - 1));
+    } else {
+#pragma unroll
+        for (int r = 0; r < 32; r++) {
+            const int i = 32 * c + r, d = d0 - r;
+            const bool ok = d >= 0 && d < K && j < ol;
+            e[r] = ok ? __ldg(links + (size_t)i * K + d) : -INFINITY;
+        }
     }
 }
 
