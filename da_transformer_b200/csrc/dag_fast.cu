@@ -40,6 +40,10 @@ constexpr int kTargetExp = 64;   // rows are rescaled with 2^-(floor(log2 max) -
 constexpr float kMaxSpread = 100.f;
 constexpr float kMinLog2Input = -100.f;  // finite links / matches below this go to the exact kernel
 
+}  // namespace dat
+#include "dag_strip.cuh"
+namespace dat {
+
 __host__ __device__ inline int fast_pitch(int L) { return (L + 127) & ~127; }
 __host__ __device__ inline int fast_rows(int L) { return (L + 15) & ~15; }
 
@@ -647,7 +651,18 @@ int dat_dag_loss_fast(const float *match_all, const float *links, const int64_t 
                                                    tarlen, prelen, translen, rows, pitch);
         if (int rc = check_launch("dat_dag_loss_fast(prep)")) return rc;
     }
-    {
+    const int strip_rp = (prelen + 63) & ~63;
+    const size_t strip_smem = strip_smem_floats(tarlen, strip_rp) * sizeof(float);
+    if (strip_smem + 512 <= (size_t)di.max_smem_optin) {
+        // all rows of a sentence fit in shared memory: strip-ordered sweep, one CTA per direction
+        if (cudaFuncSetAttribute(dag_strip_sweep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)strip_smem) != cudaSuccess)
+            return check_launch("dat_dag_loss_fast(attr)");
+        dag_strip_sweep_kernel<<<2u * (unsigned)bsz, kStripThreads, strip_smem, st>>>(
+            match_all, links, output_length, target_length, order, alpha, beta, offsets, sc.chk, sc.flag,
+            loss, status, tarlen, prelen, translen, strip_rp);
+        if (int rc = check_launch("dat_dag_loss_fast(strip sweep)")) return rc;
+    } else {
         const size_t smem = (size_t)(4 * (pitch + 32) + 2 * pitch) * sizeof(float);
         DAT_REQUIRE(smem <= (size_t)di.max_smem_optin, DAT_ERR_UNSUPPORTED,
                     "dat_dag_loss_fast: prelen=%d needs %zu bytes of shared memory", prelen, smem);
