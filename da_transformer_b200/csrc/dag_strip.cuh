@@ -192,9 +192,14 @@ __device__ __forceinline__ void strip_bulk(const float *__restrict__ links, cons
             strip_load_raw(e1, links, c, 2 * S + 1, lane, K, ol, rev);
             strip_exp_block(e0, tiny);
             strip_exp_block(e1, tiny);
+            // Warps that work on the same destination strip walk the steps in different rotations:
+            // a float atomicAdd on shared memory is a compare-and-swap loop, and warps marching
+            // through the same Pf rows in step would make each other retry.
+            const int span = to - from, rot = (warp * 7) % span;
 #pragma unroll 2
-            for (int q = from; q < to; q++) {
-                const int s = ta + q;
+            for (int q = 0; q < span; q++) {
+                int qq = q + rot; qq = qq >= span ? qq - span : qq;
+                const int s = ta + from + qq;
                 const int ec = sm.sc[(s - 1) * nH + c];
                 if (ec == kExpNone) continue;   // the block's sources are all zero at step s-1 (warp-uniform)
                 const float scale = pow2_flush(ec - sm.g[s - 1]);
