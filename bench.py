@@ -252,6 +252,7 @@ def main():
     ap.add_argument("--sentences", type=int, default=SENTENCES_PER_GPU, help="sentences per GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gather", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="launch the step kernel by kernel instead of replaying a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -294,7 +295,7 @@ def main():
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
-    def step(record=None):
+    def local_step(record=None):
         path = dag_best_alignment(match.detach(), links.detach(), ol, tl)
         if record is not None:
             record[0].record()
@@ -302,8 +303,39 @@ def main():
         if record is not None:
             record[1].record()
         gm, gl = torch.autograd.grad(loss, [match, links], grad_outputs=gout)
-        stats = ddist.all_reduce_stats(ddist.sentence_stats(loss.detach(), tl))
-        return stats, path, gm, gl
+        return ddist.sentence_stats(loss.detach(), tl), path, gm, gl
+
+    def step(record=None):
+        stats, path, gm, gl = local_step(record)
+        return ddist.all_reduce_stats(stats), path, gm, gl
+
+    # The ~30 launches of a step (ours and torch's small statistics kernels) cost more host time
+    # than the kernels take on the device, so the rank-local part of the step is captured once
+    # into a CUDA graph and replayed; the all-reduce stays an ordinary NCCL call after it.
+    graph, graph_out, launch_mode = None, None, "eager"
+    if not args.eager:
+        try:
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    local_step()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                graph_out = local_step()
+            graph, launch_mode = g, "cuda_graph"
+        except Exception as exc:   # capture not possible here: fall back to kernel-by-kernel launches
+            print(f"[bench] CUDA graph capture failed, running eagerly: {exc}", file=sys.stderr)
+            graph, graph_out = None, None
+            torch.cuda.synchronize()
+
+    def timed_step(record=None):
+        if graph is None:
+            return step(record)
+        graph.replay()
+        return ddist.all_reduce_stats(graph_out[0]), graph_out[1], graph_out[2], graph_out[3]
 
     def barrier():
         if world > 1:
@@ -329,20 +361,30 @@ def main():
     if rank == 0:
         sampler.start()
     for _ in range(args.warmup):
-        step()
+        timed_step()
     marks = [(ev(), ev()) for _ in range(args.steps)]
     barrier()
     sampler.begin()
     t0, t1 = ev(), ev()
     t0.record()
     for k in range(args.steps):
-        stats, _, _, _ = step(marks[k])
+        stats, _, _, _ = timed_step(marks[k])
     t1.record()
     barrier()
     sampler.end()
     clocks = sampler.stop() if rank == 0 else None
     elapsed_ms = t0.elapsed_time(t1)
-    sweep_ms = sum(a.elapsed_time(b) for a, b in marks) / args.steps
+    if graph is None:
+        sweep_ms = sum(a.elapsed_time(b) for a, b in marks) / args.steps
+    else:
+        # events cannot be timed inside a replayed graph: time the same forward call, same inputs,
+        # launched directly, once per timed step
+        for a, b in marks:
+            a.record()
+            dag_loss(match, links, ol, tl)
+            b.record()
+        torch.cuda.synchronize()
+        sweep_ms = sum(a.elapsed_time(b) for a, b in marks) / args.steps
     if world > 1:
         tmax = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
@@ -489,20 +531,22 @@ def main():
                          "fwd (alpha+beta) + bwd + scalar all-reduce") % B,
             "sentences_per_gpu": B, "global_sentences": B * world, "parallelism": f"dp{world}",
             "l2": "inputs (600 MB per GPU) exceed L2; no flush between steps",
+            "launch": launch_mode,
         },
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        # per step: alignment (square copy + sweep), loss forward (order, exp(links), fused sweep, check,
-        # exact fallback), loss backward (grad_match, product-form grad_links, exact fallback)
-        "gpu_launches": 10 * args.steps,
+        # per step: alignment (1: strip kernel), loss forward (4: order, strip sweep, check, exact
+        # fallback), loss backward (4: exp(links) square copy, grad_match, product-form grad_links,
+        # exact fallback)
+        "gpu_launches": 9 * args.steps,
         "roofline": {
-            "kernel": ("dag_loss forward = dag_fast_sweep_kernel (fused alpha+beta recursion) with its "
-                       "exp(links) preparation, check and fallback launches"),
+            "kernel": ("dag_loss forward = dag_strip_sweep_kernel (alpha and beta recursions, one CTA each, "
+                       "exp(links) blocks held in registers) with its order, check and fallback launches"),
             "bound": "mufu", "achieved": sweep_rate / 1e9, "peak": mufu_peak / 1e9, "unit": "Gexp/s",
             "frac": sweep_rate / mufu_peak,
-            # dram__bytes_read+write of dag_fast_sweep_kernel from the ncu capture summarised in
-            # profiles/dag_fast_sweep_c4_148sent.md (134.9 MB for 148 sentences), scaled by sentences
-            "traffic": 134.9e6 / 148 * B,
+            # dram__bytes_read+write of dag_strip_sweep_kernel from the ncu capture summarised in
+            # profiles/dag_strip_sweep_c4_148sent.md (110.2 MB for 148 sentences), scaled by sentences
+            "traffic": 110.2e6 / 148 * B,
             "peak_kind": "measured on this device by dat_probe_mufu just before the timed region",
             "nominal_peak": 16 * sm_count * peaks.get("sm_max_mhz", 1965.0) * 1e6 / 1e9,
             "algorithmic_exps_per_launch": sweep_exps, "kernel_ms": sweep_ms,

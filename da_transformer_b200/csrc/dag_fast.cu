@@ -573,6 +573,13 @@ int launch_exact_grad_links(const float *grad_output, const float *alpha, const 
                             const int64_t *target_length, float *grad_links, const int *select, int bsz,
                             int tarlen, int prelen, int translen, cudaStream_t st, const char *who);
 
+// The strip-ordered sweep keeps every row of a sentence in shared memory; when that fits it is the
+// forward path, and the square exp(links) copy is only built by the backward pass that reads it.
+static inline int strip_row_pitch(int prelen) { return (prelen + 63) & ~63; }
+static inline bool strip_applicable(int tarlen, int prelen, const DeviceInfo &di) {
+    return strip_smem_floats(tarlen, strip_row_pitch(prelen)) * sizeof(float) + 512 <= (size_t)di.max_smem_optin;
+}
+
 }  // namespace dat
 
 extern "C" {
@@ -595,6 +602,14 @@ int dat_dag_loss_backward_fast(const float *grad_output, const float *alpha, con
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int rows = fast_rows(prelen), pitch = fast_pitch(prelen);
     const FastScratch sc = carve_fast(const_cast<void *>(scratch), bsz, tarlen, prelen);
+    DeviceInfo di;
+    if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
+    if (strip_applicable(tarlen, prelen, di)) {   // the forward did not need the square exp(links): build it now
+        dim3 grid((rows + 7) / 8, bsz);
+        dag_fast_prep_kernel<<<grid, 256, 0, st>>>(links, output_length, target_length, sc.esq, sc.flag, tarlen,
+                                                   prelen, translen, rows, pitch);
+        if (int rc = check_launch("dat_dag_loss_backward_fast(prep)")) return rc;
+    }
     if (int rc = launch_grad_match(grad_output, alpha, beta, offsets, match_all, output_length,
                                    target_length, grad_match_all, bsz, tarlen, prelen, st,
                                    "dat_dag_loss_backward_fast(grad_match)"))
@@ -645,15 +660,9 @@ int dat_dag_loss_fast(const float *match_all, const float *links, const int64_t 
         output_length, target_length, sc.order, sc.flag, bsz, tarlen, prelen, do_order);
     if (int rc = check_launch("dat_dag_loss_fast(order)")) return rc;
     const int *order = do_order ? sc.order : nullptr;
-    {
-        dim3 grid((rows + 7) / 8, bsz);
-        dag_fast_prep_kernel<<<grid, 256, 0, st>>>(links, output_length, target_length, sc.esq, sc.flag,
-                                                   tarlen, prelen, translen, rows, pitch);
-        if (int rc = check_launch("dat_dag_loss_fast(prep)")) return rc;
-    }
-    const int strip_rp = (prelen + 63) & ~63;
+    const int strip_rp = strip_row_pitch(prelen);
     const size_t strip_smem = strip_smem_floats(tarlen, strip_rp) * sizeof(float);
-    if (strip_smem + 512 <= (size_t)di.max_smem_optin) {
+    if (strip_applicable(tarlen, prelen, di)) {
         // all rows of a sentence fit in shared memory: strip-ordered sweep, one CTA per direction
         if (cudaFuncSetAttribute(dag_strip_sweep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)strip_smem) != cudaSuccess)
@@ -663,6 +672,12 @@ int dat_dag_loss_fast(const float *match_all, const float *links, const int64_t 
             loss, status, tarlen, prelen, translen, strip_rp);
         if (int rc = check_launch("dat_dag_loss_fast(strip sweep)")) return rc;
     } else {
+        {
+            dim3 grid((rows + 7) / 8, bsz);
+            dag_fast_prep_kernel<<<grid, 256, 0, st>>>(links, output_length, target_length, sc.esq, sc.flag,
+                                                       tarlen, prelen, translen, rows, pitch);
+            if (int rc = check_launch("dat_dag_loss_fast(prep)")) return rc;
+        }
         const size_t smem = (size_t)(4 * (pitch + 32) + 2 * pitch) * sizeof(float);
         DAT_REQUIRE(smem <= (size_t)di.max_smem_optin, DAT_ERR_UNSUPPORTED,
                     "dat_dag_loss_fast: prelen=%d needs %zu bytes of shared memory", prelen, smem);
