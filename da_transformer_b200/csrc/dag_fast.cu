@@ -1,4 +1,6 @@
-// dag_loss forward, fast path: both recursions of a sentence in ONE CTA, in the linear
+// dag_loss forward, fast path.  When all rows of a sentence fit in shared memory the
+// strip-ordered sweep of dag_strip.cuh runs (one CTA per direction); otherwise the tiled kernel of
+// this file, described next: both recursions of a sentence in ONE CTA, in the linear
 // (probability) domain with per-row power-of-two rescaling, sharing every load of the
 // transition matrix between the alpha and the beta step.
 //
@@ -575,7 +577,8 @@ int launch_exact_grad_links(const float *grad_output, const float *alpha, const 
 
 // The strip-ordered sweep keeps every row of a sentence in shared memory; when that fits it is the
 // forward path, and the square exp(links) copy is only built by the backward pass that reads it.
-static inline int strip_row_pitch(int prelen) { return (prelen + 63) & ~63; }
+// + 4: the tensor-core operand loads of 8 consecutive rows then hit distinct banks
+static inline int strip_row_pitch(int prelen) { return ((prelen + 63) & ~63) + 4; }
 static inline bool strip_applicable(int tarlen, int prelen, const DeviceInfo &di) {
     return strip_smem_floats(tarlen, strip_row_pitch(prelen)) * sizeof(float) + 512 <= (size_t)di.max_smem_optin;
 }

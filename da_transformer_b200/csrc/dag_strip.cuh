@@ -2,27 +2,32 @@
 //
 // Both recursions only ever look one way: alpha[t][j] needs alpha[t-1][i] with i < j, and beta is
 // the same recursion on the reversed graph (vertex u = ol-1-i, step s = tl-1-t).  So a sweep can
-// finish its vertices strip by strip, every target step of a strip before the next strip, and a
+// finish its vertices group by group, every target step of a group before the next group, and a
 // 32 x 32 block of E = exp(links) then serves ALL steps while it sits in the registers of one warp
 // (lane = destination vertex, 32 source vertices per lane).  Every link is read, and
 // exponentiated, once per sweep, straight from the band: no square copy, no re-read per step.
 //
 // One CTA per (sentence, direction).  In canonical coordinates (u, s) the row of step s is
-// y[s][u] * 2^sc[s][u/32]: fp32 mantissas with one power-of-two exponent per 32 vertices, all
-// rows resident in shared memory.  For strip S (vertices 64S..64S+63):
-//   phase 1 (13 warps): items (32-vertex block c of a finished strip, step s): the dot product of
-//     y[s-1][32c..32c+31] (broadcast shared loads) with the block, for both halves of the strip
-//     at once, scaled to the step's common exponent g[s-1] and added into P[s][.].
-//   phase 2 (3 warps, one named barrier per step): the diagonal blocks depend on the strip's own
-//     previous step.  Warp 0 walks the left triangle (step s), warp 2 the square block from the
-//     left half's sources to the right half (step s), warp 1 the right triangle (step s-1).  Each
-//     combines its terms at their largest exponent, multiplies by exp(match), and renormalises
-//     with the maximum of the previous step (so the reduction is off the step-to-step chain).
+// y[s][u] * 2^sc[s][u/32]: fp32 mantissas with one power-of-two exponent per 32-vertex sub-strip,
+// all rows resident in shared memory.  Vertices are taken in groups of four sub-strips (128):
+//   phase 1 (16 warps): what the finished groups send into this group.  An item is (32-vertex
+//     source block c, 64 destination vertices, step s): the dot product of y[s-1][32c..32c+31]
+//     (broadcast shared loads) with the block, for two sub-strips at once, scaled to the step's
+//     common unit 2^g[s-1] and added into Pf[s][.].  No dependency between items.
+//   phase 2 (10 warps, one CTA barrier per iteration): the ten blocks inside the group, one per
+//     warp, walked as a pipeline.  In iteration tau the triangular block of sub-strip k does step
+//     tau - k, and the square block from sub-strip ks to kd does step tau - ks: its sources were
+//     finished one iteration earlier, and its sum (a ring accumulator with its own exponent) is
+//     complete when the destination's triangular block needs it.  A group therefore takes
+//     (steps + 3) iterations instead of 4 x steps.
+// A triangular step combines its three terms at a unit chosen from magnitudes that are known
+// before its own sum is (see strip_diag_step), multiplies by exp(match) and stores the entry; the
+// maxima it leaves behind are taken off the step-to-step chain.
 // At the end the rows are written out exactly like the other paths write them: log2 values
 // relative to one fp64 offset per row, plus the row maxima dag_fast_check_kernel needs.
-// Anything that underflows is at least 2^-126 below the largest term it is added to and at
-// least 2^-(126-64) below its own half-strip's previous maximum, which is inside what the
-// check's bound covers; inputs below 2^-100 flag the sentence as in the tiled kernel.
+// Anything that underflows is 2^-126 below the unit it is added in, which sits within 2^64 of the
+// largest term, i.e. inside what the check's bound covers; inputs below 2^-100 flag the sentence
+// as in the tiled kernel.
 #pragma once
 
 namespace dat {
@@ -127,12 +132,14 @@ constexpr int kGroupSubs = 4;                  // 32-vertex sub-strips per group
 constexpr int kGroupCols = 32 * kGroupSubs;    // 128
 constexpr int kRing = 8;                       // steps an in-group accumulator can be alive (> kGroupSubs)
 constexpr int kMRing = 32;                     // steps of match values staged ahead
+constexpr int kEtPitch = kGroupCols + 8;       // the tensor-core operand loads of a tile hit 32 distinct banks
 
 struct StripSmem {
     float *Y;       // [T][rp]            mantissas of the rows, canonical vertices
     float *Pf;      // [T][kGroupCols]    what the finished groups send to the current group, unit 2^g[s-1]
     float *M;       // [kMRing][kGroupCols] match values (natural log) of the current group, ring over steps
     float *Pr;      // [kGroupSubs][kRing][32] what the group's earlier sub-strips send, ring over steps
+    float *Et;      // [32][kEtPitch]     exp(links) from one finished 32-vertex block into the whole group
     int *Pe;        // [kGroupSubs][kRing]     and the exponent of each such accumulator
     int *sc;        // [T][nH]   exponent of each 32-vertex sub-strip (kExpNone: nothing there)
     int *g;         // [T]       largest exponent over the finished groups
@@ -142,7 +149,8 @@ struct StripSmem {
 __host__ __device__ inline size_t strip_smem_floats(int T, int rp) {
     const int nH = rp / 32;
     return (size_t)T * rp + (size_t)T * kGroupCols + (size_t)kMRing * kGroupCols +
-           (size_t)kGroupSubs * kRing * 32 + kGroupSubs * kRing + (size_t)T * nH + T + (size_t)2 * T * nH;
+           (size_t)kGroupSubs * kRing * 32 + 32 * kEtPitch + kGroupSubs * kRing + (size_t)T * nH + T +
+           (size_t)2 * T * nH;
 }
 
 // x * 2^k for k in [-252, 254] as two exact power-of-two multiplications; 0 below that range
@@ -154,62 +162,121 @@ __device__ __forceinline__ float scale2(float x, int k) {
     return (x * __int_as_float((k1 + 127) << 23)) * __int_as_float((k2 + 127) << 23);
 }
 
-// phase 1: items (32-vertex block c of a finished group, 64-vertex pair S of the current group,
-// step s), c in [cmin(S), c_last], S in [S_first, S_last], dealt to the warps in contiguous
-// ranges.  An item is the dot product of y[s-1][32c..32c+31] with the block, for both halves of
-// the pair, scaled to the step's common unit 2^g[s-1] and added into Pf.
-__device__ __forceinline__ void strip_bulk(const float *__restrict__ links, const StripSmem &sm, int S_first,
-                                           int S_last, int c_last, int warp, int lane, int K, int ol, int tl,
-                                           int W, int rp, int nH, bool rev, bool &tiny) {
-    int total = 0;
-    for (int S = S_first; S <= S_last; S++) {
-        int t0 = 64 * S - W + 1; t0 = t0 > 1 ? t0 : 1;
-        int t1 = 64 * S + 63; t1 = t1 < tl - 1 ? t1 : tl - 1;
-        int cmin = 2 * S - 1 - (K - 1) / 32; cmin = cmin > 0 ? cmin : 0;   // blocks further back hold no link into S
-        for (int c = cmin; c <= c_last; c++) {
-            int ta = 32 * c - W + 2; ta = ta > t0 ? ta : t0;
-            int tb = 32 * c + 32; tb = tb < t1 ? tb : t1;
-            total += tb >= ta ? tb - ta + 1 : 0;
+// The tensor core reads the upper 19 bits of an fp32 operand (sign, exponent, 10 mantissa bits).
+// Splitting by masking costs one logic operation; the rounding conversion instruction runs on
+// the 16-lane special-function unit and was the bottleneck of this phase.
+__device__ __forceinline__ unsigned to_tf32(float x) { return __float_as_uint(x) & 0xffffe000u; }
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// phase 1: what the finished groups send into the current group, as a matrix product on the
+// tensor cores.  For one 32-vertex source block c and all steps at once
+//     Pf[s][j] += sum_r (y[s-1][32c + r] * 2^(sc[s-1][c] - g[s-1])) * E[32c + r][32 h0 + j],  j < 128,
+// i.e. [steps x 32] x [32 x 128], summed over c.  The CTA loads and exponentiates the
+// [32 x 128] tile of E once per c (the loads of the next tile are in flight while this one is
+// used); warp w owns destination sub-strip w % 4 and the 16 steps t0 + 16 (w / 4) .. (+64 per
+// further pass), keeps its [16 x 32] result in registers over all c and stores it once: no atomics.
+// fp32 accuracy comes from splitting both operands into two tf32 numbers and adding the three
+// leading products (hi*hi + hi*lo + lo*hi) in fp32.
+// Fragment layout of mma.m16n8k8 (g8 = lane / 4, t4 = lane % 4): A rows g8, g8+8, columns t4, t4+4;
+// B rows t4, t4+4, column g8; C rows g8, g8+8, columns 2 t4, 2 t4 + 1.
+__device__ __forceinline__ void strip_bulk_mma(const float *__restrict__ links, const StripSmem &sm, int h0,
+                                               int gs, int t0, int t1, int tid, int K, int ol, int rp,
+                                               int nH, bool rev, bool &tiny) {
+    const int lane = tid & 31, warp = tid >> 5;
+    const int k = warp & 3, mt = warp >> 2, g8 = lane >> 2, t4 = lane & 3;
+    int cmin = h0 - (K - 1) / 32 - 1;   // blocks further back hold no link into the group
+    cmin = cmin > 0 ? cmin : 0;
+    // tile element q of this thread: forward rows are contiguous along the destination, reversed
+    // ones along the source, so the lanes run along that index
+    const auto tile_rc = [&](int q, int &r, int &col) {
+        if (rev) { r = lane; col = warp + kStripWarps * q; }
+        else { r = (tid >> 7) + 4 * q; col = tid & 127; }
+    };
+    const auto tile_load = [&](int c, float (&v)[8]) {
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            int r, col;
+            tile_rc(q, r, col);
+            const int up = 32 * c + r, u = 32 * h0 + col, d = u - up - 1;   // d >= 0: c < h0
+            const bool ok = d < K && u < ol;
+            const float *p = rev ? links + (size_t)(ol - 1 - (u < ol ? u : ol - 1)) * K + d
+                                 : links + (size_t)up * K + d;
+            v[q] = ok ? __ldg(p) : -INFINITY;
         }
-    }
-    const int lo = (warp * total) / kStripWarps, hi = ((warp + 1) * total) / kStripWarps;
-    int base = 0;
-    for (int S = S_first; S <= S_last; S++) {
-        int t0 = 64 * S - W + 1; t0 = t0 > 1 ? t0 : 1;
-        int t1 = 64 * S + 63; t1 = t1 < tl - 1 ? t1 : tl - 1;
-        int cmin = 2 * S - 1 - (K - 1) / 32; cmin = cmin > 0 ? cmin : 0;
-        float *pf = sm.Pf + (S - S_first) * 64;
-        for (int c = cmin; c <= c_last; c++) {
-            int ta = 32 * c - W + 2; ta = ta > t0 ? ta : t0;
-            int tb = 32 * c + 32; tb = tb < t1 ? tb : t1;
-            const int n = tb >= ta ? tb - ta + 1 : 0;
-            const int from = lo > base ? lo - base : 0;
-            const int to = hi < base + n ? hi - base : n;
-            base += n;
-            if (from >= to) continue;
-            float e0[32], e1[32];
-            strip_load_raw(e0, links, c, 2 * S, lane, K, ol, rev);   // both blocks in flight together
-            strip_load_raw(e1, links, c, 2 * S + 1, lane, K, ol, rev);
-            strip_exp_block(e0, tiny);
-            strip_exp_block(e1, tiny);
-            // Warps that work on the same destination strip walk the steps in different rotations:
-            // a float atomicAdd on shared memory is a compare-and-swap loop, and warps marching
-            // through the same Pf rows in step would make each other retry.
-            const int span = to - from, rot = (warp * 7) % span;
-#pragma unroll 2
-            for (int q = 0; q < span; q++) {
-                int qq = q + rot; qq = qq >= span ? qq - span : qq;
-                const int s = ta + from + qq;
-                const int ec = sm.sc[(s - 1) * nH + c];
-                if (ec == kExpNone) continue;   // the block's sources are all zero at step s-1 (warp-uniform)
-                const float scale = pow2_flush(ec - sm.g[s - 1]);
-                float r0, r1;
-                strip_block_dot2(sm.Y + (size_t)(s - 1) * rp + 32 * c, e0, e1, r0, r1);
-                r0 *= scale;
-                r1 *= scale;
-                if (r0 != 0.f) atomicAdd(pf + s * kGroupCols + lane, r0);
-                if (r1 != 0.f) atomicAdd(pf + s * kGroupCols + 32 + lane, r1);
+    };
+    for (int sbase = t0; sbase <= t1; sbase += 64) {   // same trip count in every warp: barriers inside
+        const int s0 = sbase + 16 * mt;
+        float acc[4][4];
+#pragma unroll
+        for (int nn = 0; nn < 4; nn++)
+#pragma unroll
+            for (int q = 0; q < 4; q++) acc[nn][q] = 0.f;
+        float nxt[8];
+        tile_load(cmin, nxt);
+        for (int c = cmin; c < h0; c++) {
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                int r, col;
+                tile_rc(q, r, col);
+                const float l2 = nxt[q] * kLog2e;
+                tiny |= (l2 < kMinLog2Input) && (l2 > -INFINITY);
+                sm.Et[r * kEtPitch + col] = ex2(l2);
             }
+            __syncthreads();
+            if (c + 1 < h0) tile_load(c + 1, nxt);
+            // scale of the two A rows this lane holds: steps s0 + g8 and s0 + g8 + 8
+            float asc[2];
+#pragma unroll
+            for (int q = 0; q < 2; q++) {
+                const int sx = s0 + g8 + 8 * q;
+                float f = 0.f;
+                if (k < gs && sx <= t1) {
+                    const int e = sm.sc[(sx - 1) * nH + c];
+                    if (e != kExpNone) f = pow2_flush(e - sm.g[sx - 1]);
+                }
+                asc[q] = f;
+            }
+            if (__any_sync(0xffffffffu, asc[0] != 0.f || asc[1] != 0.f)) {
+#pragma unroll
+                for (int kk = 0; kk < 4; kk++) {
+                    unsigned ahi[4], alo[4];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {   // (row g8 + 8 (q & 1), source t4 + 4 (q >> 1))
+                        const int sx = s0 + g8 + 8 * (q & 1);
+                        float a = 0.f;
+                        if (asc[q & 1] != 0.f)
+                            a = sm.Y[(size_t)(sx - 1) * rp + 32 * c + 8 * kk + t4 + 4 * (q >> 1)] * asc[q & 1];
+                        ahi[q] = to_tf32(a);
+                        alo[q] = to_tf32(a - __uint_as_float(ahi[q]));
+                    }
+#pragma unroll
+                    for (int nn = 0; nn < 4; nn++) {
+                        const float b0 = sm.Et[(8 * kk + t4) * kEtPitch + 32 * k + 8 * nn + g8];
+                        const float b1 = sm.Et[(8 * kk + t4 + 4) * kEtPitch + 32 * k + 8 * nn + g8];
+                        const unsigned bh0 = to_tf32(b0), bh1 = to_tf32(b1);
+                        const unsigned bl0 = to_tf32(b0 - __uint_as_float(bh0));
+                        const unsigned bl1 = to_tf32(b1 - __uint_as_float(bh1));
+                        mma_tf32(acc[nn], alo, bh0, bh1);
+                        mma_tf32(acc[nn], ahi, bl0, bl1);
+                        mma_tf32(acc[nn], ahi, bh0, bh1);
+                    }
+                }
+            }
+            __syncthreads();   // the tile is overwritten in the next round
+        }
+        if (k < gs) {
+#pragma unroll
+            for (int nn = 0; nn < 4; nn++)
+#pragma unroll
+                for (int q = 0; q < 4; q++) {   // (row g8 + 8 (q >> 1), column 2 t4 + (q & 1))
+                    const int sx = s0 + g8 + 8 * (q >> 1);
+                    if (sx <= t1) sm.Pf[sx * kGroupCols + 32 * k + 8 * nn + 2 * t4 + (q & 1)] = acc[nn][q];
+                }
         }
     }
 }
@@ -341,7 +408,8 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
     sm.Pf = sm.Y + (size_t)T * rp;
     sm.M = sm.Pf + (size_t)T * kGroupCols;
     sm.Pr = sm.M + kMRing * kGroupCols;
-    sm.Pe = reinterpret_cast<int *>(sm.Pr + kGroupSubs * kRing * 32);
+    sm.Et = sm.Pr + kGroupSubs * kRing * 32;
+    sm.Pe = reinterpret_cast<int *>(sm.Et + 32 * kEtPitch);
     sm.sc = sm.Pe + kGroupSubs * kRing;
     sm.g = sm.sc + T * nH;
     sm.mxy = reinterpret_cast<unsigned *>(sm.g + T);
@@ -403,8 +471,7 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
         stage_match(t0);
         stage_match(t0 + 8);
         // ---- phase 1: everything the finished groups send into this group
-        if (h0 > 0)
-            strip_bulk(links, sm, h0 / 2, (h0 + gs - 1) / 2, h0 - 1, warp, lane, K, ol, tl, W, rp, nH, rev, tiny);
+        if (h0 > 0) strip_bulk_mma(links, sm, h0, gs, t0, t1, tid, K, ol, rp, nH, rev, tiny);
         // ---- the group's own blocks: sub-strip pairs (ks <= kd); block n of warp w is number w + 16n
         // in the list D_0 .. D_{gs-1}, then the square blocks row by row
         float eb0[32], eb1[32];
