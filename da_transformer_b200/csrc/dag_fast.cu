@@ -56,8 +56,9 @@ struct FastScratch {
     int *order;   // [B]                sentences sorted by decreasing cost
 };
 
-__host__ __device__ inline size_t fast_scratch_bytes(int B, int T, int L) {
-    size_t e = (size_t)B * fast_rows(L) * fast_pitch(L) * sizeof(float);
+// the square matrix comes last so that a caller that does not need it (strip sweep) can leave it out
+__host__ __device__ inline size_t fast_scratch_bytes(int B, int T, int L, bool with_esq) {
+    size_t e = with_esq ? (size_t)B * fast_rows(L) * fast_pitch(L) * sizeof(float) : 0;
     size_t c = (size_t)B * 2 * T * sizeof(float);
     size_t f = (size_t)B * sizeof(int) * 2;
     return ((e + 255) & ~(size_t)255) + ((c + 255) & ~(size_t)255) + ((f + 255) & ~(size_t)255) + 256;
@@ -66,12 +67,12 @@ __host__ __device__ inline size_t fast_scratch_bytes(int B, int T, int L) {
 static inline FastScratch carve_fast(void *scratch, int B, int T, int L) {
     uintptr_t p = (reinterpret_cast<uintptr_t>(scratch) + 255) & ~(uintptr_t)255;
     FastScratch s;
-    s.esq = reinterpret_cast<float *>(p);
-    p += (((size_t)B * fast_rows(L) * fast_pitch(L) * sizeof(float)) + 255) & ~(size_t)255;
     s.chk = reinterpret_cast<float *>(p);
     p += (((size_t)B * 2 * T * sizeof(float)) + 255) & ~(size_t)255;
     s.flag = reinterpret_cast<int *>(p);
     s.order = s.flag + B;
+    p += (((size_t)B * sizeof(int) * 2) + 255) & ~(size_t)255;
+    s.esq = reinterpret_cast<float *>(p);   // only present (and only touched) on the tiled path
     return s;
 }
 
@@ -465,8 +466,8 @@ constexpr int kGK = 16;   // target steps per staging round
 __global__ void __launch_bounds__(256)
 dag_fast_grad_links_kernel(const float *__restrict__ grad_out, const float *__restrict__ alpha_all,
                            const float *__restrict__ beta_all, const double *__restrict__ offsets_all,
-                           const float *__restrict__ esq_all, const int *__restrict__ flag,
-                           const int64_t *__restrict__ output_length,
+                           const float *__restrict__ esq_all, const float *__restrict__ links_all,
+                           const int *__restrict__ flag, const int64_t *__restrict__ output_length,
                            const int64_t *__restrict__ target_length, float *__restrict__ glinks, int T,
                            int L, int K, int rows, int pitch) {
     extern __shared__ __align__(16) float gsm[];
@@ -536,15 +537,25 @@ dag_fast_grad_links_kernel(const float *__restrict__ grad_out, const float *__re
         }
     }
     const float g = live ? grad_out[b] : 0.f;
-    const float *E = esq_all + (size_t)b * rows * pitch;
+    // E[i][j] = exp(link): from the square copy when the forward built one, else straight from the band
+    const float *E = esq_all ? esq_all + (size_t)b * rows * pitch : nullptr;
+    const float *lk = links_all + (size_t)b * L * K;
 #pragma unroll
     for (int r = 0; r < 4; r++) {
         const int i = i0 + 4 * ty + r;
         if (i >= L) continue;
         float e[4] = {0.f, 0.f, 0.f, 0.f};
         if (live && i < ol) {
-            const float4 e4 = __ldg(reinterpret_cast<const float4 *>(E + (size_t)i * pitch + j0 + 4 * tx));
-            e[0] = e4.x; e[1] = e4.y; e[2] = e4.z; e[3] = e4.w;
+            if (E) {
+                const float4 e4 = __ldg(reinterpret_cast<const float4 *>(E + (size_t)i * pitch + j0 + 4 * tx));
+                e[0] = e4.x; e[1] = e4.y; e[2] = e4.z; e[3] = e4.w;
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const int j = j0 + 4 * tx + c, d = j - i - 1;
+                    if (d >= 0 && d < K && j < ol) e[c] = ex2(__ldg(lk + (size_t)i * K + d) * kLog2e);
+                }
+            }
         }
 #pragma unroll
         for (int c = 0; c < 4; c++) {
@@ -607,12 +618,9 @@ int dat_dag_loss_backward_fast(const float *grad_output, const float *alpha, con
     const FastScratch sc = carve_fast(const_cast<void *>(scratch), bsz, tarlen, prelen);
     DeviceInfo di;
     if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
-    if (strip_applicable(tarlen, prelen, di)) {   // the forward did not need the square exp(links): build it now
-        dim3 grid((rows + 7) / 8, bsz);
-        dag_fast_prep_kernel<<<grid, 256, 0, st>>>(links, output_length, target_length, sc.esq, sc.flag, tarlen,
-                                                   prelen, translen, rows, pitch);
-        if (int rc = check_launch("dat_dag_loss_backward_fast(prep)")) return rc;
-    }
+    // the strip sweep builds no square exp(links) copy: the gradient kernel then exponentiates the band entry
+    // it is about to overwrite with the gradient's twin anyway (same address pattern as its store)
+    const float *esq = strip_applicable(tarlen, prelen, di) ? nullptr : sc.esq;
     if (int rc = launch_grad_match(grad_output, alpha, beta, offsets, match_all, output_length,
                                    target_length, grad_match_all, bsz, tarlen, prelen, st,
                                    "dat_dag_loss_backward_fast(grad_match)"))
@@ -620,7 +628,7 @@ int dat_dag_loss_backward_fast(const float *grad_output, const float *alpha, con
     {
         dim3 grid((prelen + translen + kGT - 1) / kGT, (prelen + kGT - 1) / kGT, bsz);
         const size_t smem = (size_t)(2 * kGK * kGT + tarlen) * sizeof(float);
-        dag_fast_grad_links_kernel<<<grid, 256, smem, st>>>(grad_output, alpha, beta, offsets, sc.esq,
+        dag_fast_grad_links_kernel<<<grid, 256, smem, st>>>(grad_output, alpha, beta, offsets, esq, links,
                                                             sc.flag, output_length, target_length,
                                                             grad_links, tarlen, prelen, translen, rows,
                                                             pitch);
@@ -634,7 +642,10 @@ int dat_dag_loss_backward_fast(const float *grad_output, const float *alpha, con
 
 size_t dat_dag_loss_fast_scratch_bytes(int bsz, int tarlen, int prelen) {
     if (bsz <= 0 || tarlen <= 0 || prelen <= 0) return 0;
-    return dat::fast_scratch_bytes(bsz, tarlen, prelen);
+    // the square exp(links) matrix is only needed when the tiled sweep runs on the current device
+    dat::DeviceInfo di;
+    const bool with_esq = !dat::device_info(&di) || !dat::strip_applicable(tarlen, prelen, di);
+    return dat::fast_scratch_bytes(bsz, tarlen, prelen, with_esq);
 }
 
 int dat_dag_loss_fast(const float *match_all, const float *links, const int64_t *output_length,

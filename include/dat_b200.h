@@ -116,10 +116,12 @@ int dat_dag_loss(const float *match_all, const float *links, const int64_t *outp
  * Fast path of `dag_loss` with require_gradient (replaces the same reference function as
  * dat_dag_loss: dag_loss.cpp:19; dag_loss.cu:313-375).  Same outputs and the same workspace
  * format as dat_dag_loss(..., require_gradient = 1, ...), so dat_dag_loss_backward consumes them
- * unchanged.  The recursions run in the probability domain on E = exp(links), computed once
- * per call into `scratch` (dat_dag_loss_fast_scratch_bytes bytes, caller-allocated, contents
- * irrelevant on entry; it also holds what dat_dag_loss_backward_fast reuses).  Per-row
- * rescaling keeps ~160 binades below each row maximum; an a-posteriori bound on the mass that
+ * unchanged.  The recursions run in the probability domain on E = exp(links), each link
+ * exponentiated once per sweep instead of once per target step.  `scratch`
+ * (dat_dag_loss_fast_scratch_bytes bytes for the current device, caller-allocated, contents
+ * irrelevant on entry) holds what dat_dag_loss_backward_fast reuses: the per-sentence flags and
+ * row maxima and, for sentences too large to keep their rows in shared memory, a square copy
+ * of E.  Power-of-two rescaling keeps ~160 binades below the largest term; an a-posteriori bound on the mass that
  * could have been flushed decides per sentence whether the result is kept or the sentence is
  * recomputed by the exact log-domain kernel inside the same call, so the result always meets
  * the tolerances of dat_dag_loss.
