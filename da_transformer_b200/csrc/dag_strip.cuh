@@ -415,17 +415,6 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
     sm.mxy = reinterpret_cast<unsigned *>(sm.g + T);
     sm.mxv = sm.mxy + T * nH;
 
-    // ask L2 for the sentence's links (the rows' existing entries) and match rows now; the block
-    // loads later find them there
-    for (int i = tid; i < ol - 1; i += kStripThreads) {
-        const int n = ol - 1 - i < K ? ol - 1 - i : K;   // entries of row i that exist
-        const char *row = reinterpret_cast<const char *>(links + (size_t)i * K);
-        for (int off = 0; off < n * 4; off += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + off));
-    }
-    for (int x = tid; x < tl * ((L * 4 + 127) / 128); x += kStripThreads) {
-        const int t = x / ((L * 4 + 127) / 128), seg = x % ((L * 4 + 127) / 128);
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char *>(match + (size_t)t * L) + seg * 128));
-    }
     for (int x = tid; x < tl * rp; x += kStripThreads) sm.Y[x] = 0.f;
     for (int x = tid; x < T * kGroupCols; x += kStripThreads) sm.Pf[x] = 0.f;
     for (int x = tid; x < kGroupSubs * kRing * 32; x += kStripThreads) sm.Pr[x] = 0.f;
