@@ -54,6 +54,9 @@ def check_dag_against_oracle(batch, grad_out=None):
 @pytest.mark.parametrize("seed,B,L,T,K", [
     (1, 5, 24, 6, None), (2, 4, 40, 9, 6), (3, 3, 33, 7, None), (4, 6, 97, 13, None),
     (5, 2, 130, 31, 40), (6, 3, 64, 2, None), (7, 2, 200, 50, None), (8, 4, 32, 32, None),
+    # more than 64 target steps with all rows still in shared memory (strip sweep, two passes of its
+    # matrix-product phase), full and banded links
+    (9, 2, 190, 100, None), (10, 2, 190, 100, 40),
 ])
 def test_dag_loss_matches_oracle(seed, B, L, T, K):
     batch = workloads.small_batch(seed=seed, B=B, L=L, T=T, V=50, translen=K)
@@ -94,7 +97,7 @@ def test_forced_alignment_match_with_minus_inf_and_zero():
 @pytest.mark.parametrize("config", [1, 2, 3, 4])
 @pytest.mark.parametrize("seed,B,L,T,K,quant", [
     (1, 5, 24, 6, None, 0), (2, 4, 40, 9, 6, 0), (3, 4, 70, 12, None, 0.5), (4, 3, 97, 13, 20, 1.0),
-    (5, 2, 160, 20, None, 0.25), (6, 2, 64, 5, None, 2.0),
+    (5, 2, 160, 20, None, 0.25), (6, 2, 64, 5, None, 2.0), (7, 2, 190, 100, None, 0.5), (8, 2, 190, 100, 40, 0.5),
 ])
 def test_best_alignment_bit_exact(config, seed, B, L, T, K, quant):
     batch = workloads.small_batch(seed=seed, B=B, L=L, T=T, V=50, translen=K)
