@@ -536,8 +536,8 @@ def main():
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         # per step: alignment (1: strip kernel), loss forward (4: order, strip sweep, check, exact
-        # fallback), loss backward (3: grad_match, product-form grad_links, exact fallback)
-        "gpu_launches": 8 * args.steps,
+        # fallback), loss backward (3: grad_match, product-form grad_links, exact fallback), statistics (1)
+        "gpu_launches": 9 * args.steps,
         "roofline": {
             "kernel": ("dag_loss forward = dag_strip_sweep_kernel (alpha and beta recursions, one CTA each, "
                        "exp(links) blocks held in registers) with its order, check and fallback launches"),

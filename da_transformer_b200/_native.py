@@ -20,7 +20,7 @@ EXPORTS = (
     "dat_version", "dat_last_error", "dat_status_string", "dat_dag_loss_offsets_bytes",
     "dat_dag_best_alignment_workspace_bytes", "dat_logsoftmax_gather",
     "dat_logsoftmax_gather_backward", "dat_dag_loss", "dat_dag_loss_backward",
-    "dat_dag_best_alignment", "dat_probe_mufu", "dat_dag_loss_static",
+    "dat_dag_best_alignment", "dat_probe_mufu", "dat_dag_loss_static", "dat_sentence_stats",
     "dat_dag_loss_fast", "dat_dag_loss_fast_scratch_bytes", "dat_dag_loss_backward_fast",
 )
 
@@ -60,6 +60,8 @@ def _declare(lib):
     lib.dat_dag_loss_backward_fast.argtypes = [_vp] * 11 + [_i32] * 4 + [_vp]
     lib.dat_probe_mufu.restype = _i32
     lib.dat_probe_mufu.argtypes = [_i32, _i32, _vp, _vp]
+    lib.dat_sentence_stats.restype = _i32
+    lib.dat_sentence_stats.argtypes = [_vp, _vp, _vp, _i32, _vp]
 
 
 def lib():

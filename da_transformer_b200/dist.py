@@ -24,14 +24,26 @@ def sentence_stats(loss_result: torch.Tensor, target_length: torch.Tensor) -> to
     ``[sum_b loss_b / tl_b, sum_b tl_b, n_sentences, n_invalid]``.
 
     Mirrors fs_plugins/criterions/nat_dag_loss.py:190-194: sentences whose
-    log-likelihood is inf/nan are zeroed and counted as invalid.  No host sync."""
+    log-likelihood is inf/nan are zeroed and counted as invalid.  No host sync.
+    On the GPU this is one launch of the library (``dat_sentence_stats``) instead of a dozen
+    elementwise and reduction launches; CPU tensors (the gloo tests of the multi-process glue)
+    take the same expression in torch ops."""
+    if loss_result.is_cuda:
+        from . import _native
+        loss32 = loss_result.detach().to(torch.float32).contiguous()
+        tl64 = target_length.to(torch.int64).contiguous()
+        stats = torch.empty(4, dtype=torch.float64, device=loss_result.device)
+        _native.check(_native.lib().dat_sentence_stats(
+            _native.ptr(loss32), _native.ptr(tl64), _native.ptr(stats), int(loss32.numel()),
+            _native.stream_ptr(loss_result.device)), "dat_sentence_stats")
+        return stats
     invalid = loss_result.isinf().logical_or(loss_result.isnan())
     clean = loss_result.masked_fill(invalid, 0).to(torch.float64)
     tl = target_length.to(torch.float64)
     return torch.stack([
         (clean / tl).sum(),
         tl.sum(),
-        clean.new_full((), float(loss_result.numel())),   # a fill kernel: no host-to-device copy, no sync
+        clean.new_full((), float(loss_result.numel())),
         invalid.sum().to(torch.float64),
     ])
 

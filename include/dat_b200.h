@@ -205,6 +205,17 @@ int dat_dag_best_alignment(const float *match_all, const float *links,
  */
 int dat_probe_mufu(int iters, int blocks, float *sink, void *stream);
 
+/*
+ * Per-shard statistics of the criterion in one launch (replaces the elementwise and reduction
+ * launches of fs_plugins/criterions/nat_dag_loss.py:190-194 that follow dag_loss, and produces the
+ * fp64 buffer the reference all-reduces, fairseq/distributed/utils.py:634-680):
+ *   stats[0] = sum_b loss_b / target_length_b over the sentences whose loss is finite,
+ *   stats[1] = sum_b target_length_b, stats[2] = bsz, stats[3] = number of sentences with inf/nan loss.
+ * loss: [bsz] fp32, target_length: [bsz] int64, stats: [4] fp64, all on the device.
+ */
+int dat_sentence_stats(const float *loss, const int64_t *target_length, double *stats, int bsz,
+                       void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -433,3 +433,22 @@ def test_c1_shaped_chain_with_fp16_logits(dag_loss_path):
         pos = np.nonzero(p[b] >= 0)[0]
         assert p[b][pos].tolist() == list(range(int(tl[b]))) and pos[-1] == int(ol[b]) - 1
     assert torch.isfinite(links.grad).all() and (links.grad <= 0).all()   # d(-loss)/d links <= 0
+
+
+@pytest.mark.gpu
+def test_sentence_stats_kernel_matches_the_criterion_expression():
+    """fs_plugins/criterions/nat_dag_loss.py:190-194: inf/nan likelihoods are zeroed and counted."""
+    from da_transformer_b200 import dist as ddist
+    gen = torch.Generator().manual_seed(5)
+    for B in (1, 7, 512, 3000):
+        loss = -torch.rand(B, generator=gen) * 900
+        tl = torch.randint(2, 65, (B,), generator=gen)
+        if B >= 7:
+            loss[1] = float("-inf")
+            loss[3] = float("nan")
+            loss[B - 1] = float("inf")
+        want = ddist.sentence_stats(loss, tl)                       # torch expression (CPU tensors)
+        got = ddist.sentence_stats(loss.to(DEV), tl.to(DEV)).cpu()  # one launch of the library
+        assert got.dtype == torch.float64
+        assert torch.equal(got[1:], want[1:])
+        assert abs(float(got[0] - want[0])) <= 1e-9 * max(1.0, abs(float(want[0])))
