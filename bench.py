@@ -295,15 +295,30 @@ def main():
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
-    def local_step(record=None):
-        path = dag_best_alignment(match.detach(), links.detach(), ol, tl)
+    # The alignment and the loss only read match and links, so they are independent: inside the
+    # captured graph the alignment is a parallel branch (a second stream during capture) and its
+    # last, partly filled wave of CTAs overlaps the loss kernels.  Kernel-by-kernel launches keep one
+    # stream (cross-stream tensor reuse made them slower, not faster).
+    align_stream = torch.cuda.Stream(device=dev)
+
+    def local_step(record=None, fork=False):
+        cur = torch.cuda.current_stream(dev)
+        if fork:
+            align_stream.wait_stream(cur)
+            with torch.cuda.stream(align_stream):
+                path = dag_best_alignment(match.detach(), links.detach(), ol, tl)
+        else:
+            path = dag_best_alignment(match.detach(), links.detach(), ol, tl)
         if record is not None:
             record[0].record()
         loss = dag_loss(match, links, ol, tl)
         if record is not None:
             record[1].record()
         gm, gl = torch.autograd.grad(loss, [match, links], grad_outputs=gout)
-        return ddist.sentence_stats(loss.detach(), tl), path, gm, gl
+        stats = ddist.sentence_stats(loss.detach(), tl)
+        if fork:
+            cur.wait_stream(align_stream)
+        return stats, path, gm, gl
 
     def step(record=None):
         stats, path, gm, gl = local_step(record)
@@ -324,7 +339,7 @@ def main():
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
-                graph_out = local_step()
+                graph_out = local_step(fork=True)
             graph, launch_mode = g, "cuda_graph"
         except Exception as exc:   # capture not possible here: fall back to kernel-by-kernel launches
             print(f"[bench] CUDA graph capture failed, running eagerly: {exc}", file=sys.stderr)
