@@ -459,26 +459,24 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
         };
         stage_match(t0);
         stage_match(t0 + 8);
-        // ---- phase 1: everything the finished groups send into this group
-        if (h0 > 0) strip_bulk_mma(links, sm, h0, gs, t0, t1, tid, K, ol, rp, nH, rev, tiny);
-        // ---- the group's own blocks: sub-strip pairs (ks <= kd); block n of warp w is number w + 16n
-        // in the list D_0 .. D_{gs-1}, then the square blocks row by row
-        float eb0[32], eb1[32];
-        int ks0 = -1, kd0 = -1, ks1 = -1, kd1 = -1;
+        // ---- the group's own blocks: sub-strip pairs (ks <= kd); warp w takes block number w of the
+        // list D_0 .. D_{gs-1}, then the square blocks row by row.  Its links are requested now and
+        // exponentiated after phase 1, which hides their latency.
+        static_assert(kGroupSubs * (kGroupSubs + 1) / 2 <= kStripWarps, "one block per warp");
+        float eb0[32];
+        int ks0 = -1, kd0 = -1;
         {
             int idx = 0;
             for (int kd = 0; kd < gs; kd++, idx++)
                 if (idx == warp) { ks0 = kd; kd0 = kd; }
             for (int kd = 1; kd < gs; kd++)
-                for (int ks = 0; ks < kd; ks++, idx++) {
+                for (int ks = 0; ks < kd; ks++, idx++)
                     if (idx == warp) { ks0 = ks; kd0 = kd; }
-                    if (idx == warp + kStripWarps) { ks1 = ks; kd1 = kd; }
-                }
         }
         if (kd0 >= 0) strip_load_raw(eb0, links, h0 + ks0, h0 + kd0, lane, K, ol, rev);
-        if (kd1 >= 0) strip_load_raw(eb1, links, h0 + ks1, h0 + kd1, lane, K, ol, rev);
+        // ---- phase 1: everything the finished groups send into this group
+        if (h0 > 0) strip_bulk_mma(links, sm, h0, gs, t0, t1, tid, K, ol, rp, nH, rev, tiny);
         if (kd0 >= 0) strip_exp_block(eb0, tiny);
-        if (kd1 >= 0) strip_exp_block(eb1, tiny);
         strip_cp_async_wait_all();
         __syncthreads();
         // ---- phase 2: pipelined walk.  In iteration tau the diagonal block of sub-strip k does step
@@ -502,10 +500,6 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
                     if (ks0 == kd0) strip_diag_step(sm, eb0, h0 + kd0, kd0, s, lane, ol, W, rp, nH, rev, cy, tiny);
                     else strip_cross_step(sm, eb0, h0, ks0, kd0, s, lane, rp, nH);
                 }
-            }
-            if (kd1 >= 0) {
-                const int s = tau - ks1;
-                if (s >= t0 && s <= t1) strip_cross_step(sm, eb1, h0, ks1, kd1, s, lane, rp, nH);
             }
             __syncthreads();
         }
