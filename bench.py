@@ -559,8 +559,8 @@ def main():
             "bound": "mufu", "achieved": sweep_rate / 1e9, "peak": mufu_peak / 1e9, "unit": "Gexp/s",
             "frac": sweep_rate / mufu_peak,
             # dram__bytes_read+write of dag_strip_sweep_kernel from the ncu capture summarised in
-            # profiles/dag_strip_sweep_c4_148sent.md (108.6 MB for 148 sentences), scaled by sentences
-            "traffic": 108.6e6 / 148 * B,
+            # profiles/dag_strip_sweep_c4_148sent.md (108.7 MB for 148 sentences), scaled by sentences
+            "traffic": 108.7e6 / 148 * B,
             "peak_kind": "measured on this device by dat_probe_mufu just before the timed region",
             "nominal_peak": 16 * sm_count * peaks.get("sm_max_mhz", 1965.0) * 1e6 / 1e9,
             "algorithmic_exps_per_launch": sweep_exps, "kernel_ms": sweep_ms,
