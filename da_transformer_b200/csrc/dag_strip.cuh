@@ -10,10 +10,10 @@
 // One CTA per (sentence, direction).  In canonical coordinates (u, s) the row of step s is
 // y[s][u] * 2^sc[s][u/32]: fp32 mantissas with one power-of-two exponent per 32-vertex sub-strip,
 // all rows resident in shared memory.  Vertices are taken in groups of four sub-strips (128):
-//   phase 1 (16 warps): what the finished groups send into this group.  An item is (32-vertex
-//     source block c, 64 destination vertices, step s): the dot product of y[s-1][32c..32c+31]
-//     (broadcast shared loads) with the block, for two sub-strips at once, scaled to the step's
-//     common unit 2^g[s-1] and added into Pf[s][.].  No dependency between items.
+//   phase 1 (16 warps, tensor cores): what the finished groups send into this group.  For each
+//     finished 32-vertex source block c this is, over all steps at once, the product
+//     [steps x 32] x [32 x 128] of the rows y[s-1][32c..32c+31] (scaled to the step's common unit
+//     2^g[s-1]) with the tile of E; see strip_bulk_mma.  No dependency between source blocks.
 //   phase 2 (10 warps, one CTA barrier per iteration): the ten blocks inside the group, one per
 //     warp, walked as a pipeline.  In iteration tau the triangular block of sub-strip k does step
 //     tau - k, and the square block from sub-strip ks to kd does step tau - ks: its sources were
@@ -34,8 +34,6 @@ namespace dat {
 
 constexpr int kStripThreads = 512;
 constexpr int kStripWarps = kStripThreads / 32;
-constexpr int kStripDiagWarps = 3;
-constexpr int kStripBulkWarps = kStripWarps - kStripDiagWarps;
 constexpr int kExpNone = -(1 << 28);   // exponent of a half-strip that is entirely zero
 
 // 2^k as a float; 0 when it would be subnormal or when an operand was kExpNone
@@ -54,10 +52,6 @@ __device__ __forceinline__ void strip_cp_async4(float *smem_dst, const float *gs
 __device__ __forceinline__ void strip_cp_async_wait_all() {
     asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
-__device__ __forceinline__ void strip_diag_sync() {
-    asm volatile("bar.sync 1, %0;" ::"n"(kStripDiagWarps * 32) : "memory");
-}
-
 // l[r] = link (natural log) from canonical vertex 32c+r to canonical vertex 32h+lane, -inf if it
 // does not exist.  Forward: links[u'][u-u'-1]; reversed: the link of the original graph from
 // ol-1-u to ol-1-u', i.e. links[ol-1-u][u-u'-1].  A block strictly before the diagonal whose every
@@ -90,12 +84,6 @@ __device__ __forceinline__ void strip_exp_block(float (&e)[32], bool &tiny) {
         e[r] = ex2(l2);
     }
 }
-__device__ __forceinline__ void strip_load_block(float (&e)[32], const float *__restrict__ links, int c,
-                                                 int h, int lane, int K, int ol, bool rev, bool &tiny) {
-    strip_load_raw(e, links, c, h, lane, K, ol, rev);
-    strip_exp_block(e, tiny);
-}
-
 __device__ __forceinline__ float strip_block_dot(const float *yrow, const float (&e)[32]) {
     float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
@@ -107,25 +95,6 @@ __device__ __forceinline__ float strip_block_dot(const float *yrow, const float 
         s3 = fmaf(a.w, e[4 * q + 3], s3);
     }
     return (s0 + s1) + (s2 + s3);
-}
-
-__device__ __forceinline__ void strip_block_dot2(const float *yrow, const float (&e0)[32],
-                                                 const float (&e1)[32], float &r0, float &r1) {
-    float s0 = 0.f, s1 = 0.f, v0 = 0.f, v1 = 0.f;
-#pragma unroll
-    for (int q = 0; q < 8; q++) {
-        const float4 a = *reinterpret_cast<const float4 *>(yrow + 4 * q);
-        s0 = fmaf(a.x, e0[4 * q], s0);
-        s1 = fmaf(a.y, e0[4 * q + 1], s1);
-        v0 = fmaf(a.x, e1[4 * q], v0);
-        v1 = fmaf(a.y, e1[4 * q + 1], v1);
-        s0 = fmaf(a.z, e0[4 * q + 2], s0);
-        s1 = fmaf(a.w, e0[4 * q + 3], s1);
-        v0 = fmaf(a.z, e1[4 * q + 2], v0);
-        v1 = fmaf(a.w, e1[4 * q + 3], v1);
-    }
-    r0 = s0 + s1;
-    r1 = v0 + v1;
 }
 
 constexpr int kGroupSubs = 4;                  // 32-vertex sub-strips per group
