@@ -125,6 +125,7 @@ __host__ __device__ inline size_t strip_smem_floats(int T, int rp) {
 // x * 2^k for k in [-252, 254] as two exact power-of-two multiplications; 0 below that range
 // (also for k derived from kExpNone)
 __device__ __forceinline__ float scale2(float x, int k) {
+    if (k >= -126 && k <= 127) return x * __int_as_float((k + 127) << 23);   // the usual case: one factor
     if (k < -252) return 0.f;
     k = k > 254 ? 254 : k;
     const int k1 = k / 2, k2 = k - k1;
@@ -302,7 +303,7 @@ __device__ __forceinline__ void strip_diag_step(const StripSmem &sm, const float
     float a1 = 0.f, a2 = 0.f;
     if (eo != kExpNone && est != kExpNone && eo - sn >= -252) {
         int kk = eo - sn; kk = kk > 254 ? 254 : kk;
-        const int k1 = kk / 2;
+        const int k1 = (kk >= -126 && kk <= 127) ? kk : kk / 2;   // the usual case: one factor, the other is 1
         a1 = __int_as_float((k1 + 127) << 23);
         a2 = __int_as_float((kk - k1 + 127) << 23);
     }
