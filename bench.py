@@ -1,29 +1,36 @@
 """Benchmark of the DA-Transformer custom-op hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--scaling weak|strong]
     (N > 1: python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...)
 
-Workload (configuration C4): every GPU holds 512 sentences with graph length L=512
-(= output_length), target_length ~ U{32..64} padded to T=64, fp32 links and fp32 match
-(match has the distribution log-softmax over V=42000 bf16 N(0,2) logits gives at the
-target tokens).  One step = dag_best_alignment + dag_loss forward (alpha+beta) +
-dag_loss backward over the rank's sentences, then the SUM all-reduce of the scalar
-statistics.  Per-GPU work is fixed as N grows (weak scaling); no tensor crosses GPUs.
-The inputs (600 MB per GPU) are larger than L2, so no flush is needed between steps.
+Workload (configuration C4): sentences with graph length L=512 (= output_length), target_length
+~ U{32..64} padded to T=64, fp32 links and fp32 match (match has the distribution log-softmax over
+V=42000 bf16 N(0,2) logits gives at the target tokens).  One step = dag_best_alignment + dag_loss
+forward (alpha+beta) + dag_loss backward over the rank's sentences + the criterion's statistics,
+then the SUM all-reduce of those statistics.  No tensor crosses GPUs.
 
-`value` is sentences/s with the inputs resident in HBM; `e2e` is the same step through
-the public Python API with inputs copied from pinned host memory and the statistics
-copied back every step.  `roofline` describes the dominant kernel (the alpha/beta sweep):
-algorithmic special-function evaluations per launch (one exp per (t, i->j) term of the
-log-domain recursion, the reference's formulation) over its CUDA-event duration, against
-the special-function throughput measured on this device just before.  The shipped forward
-runs the recursion in the probability domain and spends one FFMA per term instead, so the
-fraction may exceed 1.  `gather` reports
-logsoftmax_gather forward+backward on the C2 shape against the measured HBM copy
-bandwidth.  `cpu_baseline` is the CPU oracle (a port of the reference's arithmetic) timed
-on this host's cores on a bounded sample.
+Headline (`value`): weak scaling, every GPU holds 512 sentences (600 MB of inputs per GPU, larger
+than L2, so no flush is needed between steps).  The line also carries a `strong` block: the same
+step on 512 / N sentences per GPU, i.e. ONE 512-sentence batch split over the N GPUs; `--scaling
+strong` makes that the headline instead.
+
+The timed region of K steps is repeated `--repeats` times (barrier + synchronize around each);
+`ms_per_step` is the median region divided by K, min and max are reported beside it.
+
+`e2e` is the same step through the public Python API with inputs copied from pinned host memory
+and the statistics copied back every step.  `roofline` describes the dominant kernel (the
+alpha/beta sweep of the loss forward) from the median of direct launches on preallocated buffers:
+algorithmic special-function evaluations per launch (one exp per (t, i->j) term of the log-domain
+recursion, the reference's formulation) against the special-function throughput measured on this
+device just before; `roofline_shipped` is the work the shipped probability-domain kernel executes
+(FFMA and tf32 tensor-core products) against the measured FP32 and nominal TF32 peaks.
+`gather` reports logsoftmax_gather forward+backward on all six C2 cases against the measured HBM
+copy bandwidth.  `configs` holds the step times of C1 and C3.  `cpu_baseline` is the CPU oracle (a
+C port of the reference's arithmetic) and `cpu_baseline_torch` the torch-native twin, both timed on
+this host's cores on a bounded sample.
 """
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -38,7 +45,7 @@ if ROOT not in sys.path:
 
 METRIC = "dag_loss_fwd_bwd_sentences_per_s"
 UNIT = "sentences/s"
-SENTENCES_PER_GPU = 512
+GLOBAL_SENTENCES = 512
 L_GRAPH, T_MAX, VOCAB = 512, 64, 42000
 
 
@@ -48,6 +55,13 @@ def measured_peaks():
         with open(path) as f:
             return json.load(f), "measured"
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "sm_max_mhz": 1965.0}, "fallback"
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
 def exp_counts(ol, tl, K):
@@ -65,11 +79,29 @@ def exp_counts(ol, tl, K):
     return float(sweeps.sum()), float(total.sum())
 
 
+def shipped_work(ol, tl):
+    """What dag_strip_sweep_kernel executes per launch (both directions): vertices are taken in groups
+    of 128 (four 32-vertex sub-strips); the 10 blocks of 32 x 32 inside a group run as FFMAs once per
+    target step, every block outside runs on the tensor cores as three tf32 products (3xTF32)."""
+    ffma = mma = 0.0
+    for o, t in zip(ol.tolist(), tl.tolist()):
+        nsub = (o + 31) // 32
+        groups = (nsub + 3) // 4
+        in_group_blocks = 0
+        for g in range(groups):
+            gs = min(4, nsub - 4 * g)
+            in_group_blocks += gs * (gs + 1) // 2
+        all_blocks = nsub * (nsub + 1) // 2
+        ffma += 2.0 * (t - 1) * in_group_blocks * 1024
+        mma += 2.0 * (t - 1) * (all_blocks - in_group_blocks) * 1024 * 3
+    return ffma, mma
+
+
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi.  It is started well before the
-    timed region (its start-up talks to the driver for tens of milliseconds and would stall
-    kernel launches if it overlapped the region); the samples whose timestamps fall inside the
-    region are the ones reported."""
+    """Samples SM clock and throttle reasons with nvidia-smi (query only).  Started well before the
+    timed regions (its start-up talks to the driver for tens of milliseconds and would stall kernel
+    launches if it overlapped them); the samples whose timestamps fall inside the regions are the ones
+    reported."""
     QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -123,23 +155,25 @@ class ClockSampler:
                 continue
             try:
                 ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
-                rows.append((ts, float(parts[1]), float(parts[2]),
+                rows.append((ts, float(parts[1]), float(parts[2]), float(parts[3]),
                              [n for n, v in zip(names, parts[5:9]) if v.lower().startswith("active")]))
             except ValueError:
                 continue
         inside = [r for r in rows if self.t_begin is not None and self.t_begin - 0.02 <= r[0] <= self.t_end + 0.02]
-        where = "timed region"
+        where = "timed regions"
         if not inside:   # clock skew between nvidia-smi's timestamps and this process: use all samples
-            inside, where = rows, "whole run (no sample carried a timestamp inside the region)"
+            inside, where = rows, "whole run (no sample carried a timestamp inside the regions)"
         sm = [r[1] for r in inside]
-        reasons = sorted({x for r in inside for x in r[3]})
+        reasons = sorted({x for r in inside for x in r[4]})
         return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_min_mhz": min(sm) if sm else None,
                 "sm_max_mhz": max(r[2] for r in inside) if inside else None,
+                "power_w_max": max(r[3] for r in inside) if inside else None,
                 "samples": len(sm), "window": where, "reasons": reasons}
 
 
 # --------------------------------------------------------------------------------------
-# CPU arm: the oracle (a port of the reference's arithmetic), all host threads
+# CPU arm: the oracle (a C port of the reference's arithmetic) and the torch-native twin
 # --------------------------------------------------------------------------------------
 def cpu_step(batch_np):
     from oracle import oracle
@@ -159,8 +193,16 @@ def cpu_sample(n):
     return (b.match_all.numpy(), b.links.numpy(), b.output_length.numpy(), b.target_length.numpy())
 
 
+def cpu_threads_setup():
+    """All host threads for the oracle's OpenMP loops, whatever OMP_NUM_THREADS the launcher exported
+    (torchrun sets it to 1 for N > 1).  Returns the number of threads the loops will really use."""
+    from oracle import oracle
+
+    return oracle.set_threads(host_threads())
+
+
 def cpu_baseline(budget_s=12.0):
-    cores = os.cpu_count() or 1
+    cores = cpu_threads_setup()
     sample = cpu_sample(cores)
     t0 = time.perf_counter()
     cpu_step(sample)                       # also warms the thread pool
@@ -172,7 +214,41 @@ def cpu_baseline(budget_s=12.0):
     dt = (time.perf_counter() - t0) / reps
     return {"value": cores / dt, "unit": UNIT, "cores": cores, "kind": "port",
             "sample": f"{cores} C4 sentences (L=512, T=64) per pass, {reps} passes, fp32 oracle "
-                      f"(oracle/dag_oracle.c, OpenMP over sentences): best alignment + alpha + beta + backward"}
+                      f"(oracle/dag_oracle.c, OpenMP over sentences, omp_get_max_threads() = {cores}): "
+                      f"best alignment + alpha + beta + backward"}
+
+
+def cpu_baseline_torch(n=8, budget_s=10.0):
+    """The torch-native twin (this package's torch_dag_loss / torch_dag_best_alignment, which follow
+    the reference's torch path, fs_plugins/custom_ops/dag_loss.py:259-353, and are checked against
+    fixtures made by it) on the same kind of sample, all host threads."""
+    import torch
+
+    from da_transformer_b200 import torch_twins, workloads
+
+    cores = host_threads()
+    torch.set_num_threads(cores)
+    b = workloads.config4(B=n)
+    sq = workloads.band_to_square(b.links)
+
+    def step():
+        m = b.match_all.clone().requires_grad_()
+        l = sq.clone().requires_grad_()
+        torch_twins.torch_dag_best_alignment(m.detach(), l.detach(), b.output_length, b.target_length)
+        loss = torch_twins.torch_dag_loss(m, l, b.output_length, b.target_length)
+        torch.autograd.grad(loss.sum(), [m, l])
+
+    t0 = time.perf_counter()
+    step()
+    one = time.perf_counter() - t0
+    reps = max(1, min(5, int(budget_s / max(one, 1e-3))))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        step()
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": n / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{n} C4 sentences per pass, {reps} passes, fp32 torch-native twin "
+                      f"(da_transformer_b200/torch_twins.py): best alignment + loss + autograd backward"}
 
 
 def reference_cuda_baseline(match, links, ol, tl, gout, iters=5):
@@ -216,7 +292,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cores = os.cpu_count() or 1
+    cores = cpu_threads_setup()
     n = cores
     sample = cpu_sample(n)
     for _ in range(max(1, min(args.warmup, 1))):
@@ -226,12 +302,13 @@ def run_reference(args):
         cpu_step(sample)
     dt = time.perf_counter() - t0
     value = n * args.steps / dt
-    desc = (f"{n} C4 sentences per step on {cores} host threads, fp32 CPU oracle port of the reference "
-            f"arithmetic (the reference's own CPU path is PyTorch code that cannot travel to this box)")
+    desc = (f"{n} C4 sentences per step on {cores} host threads (omp_get_max_threads(), set explicitly), fp32 CPU "
+            f"oracle port of the reference arithmetic (the reference's own CPU path is PyTorch code that cannot "
+            f"travel to this box)")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
         "config": {"workload": "C4 sample: L=512, T=64, tl~U{32..64}, dag_best_alignment + dag_loss fwd+bwd",
                    "sentences_per_step": n},
@@ -248,13 +325,18 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--repeats", type=int, default=10, help="how many times the K-step timed region is repeated")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--sentences", type=int, default=SENTENCES_PER_GPU, help="sentences per GPU")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: 512 sentences per GPU; strong: one 512-sentence batch split over the GPUs")
+    ap.add_argument("--sentences", type=int, default=None, help="sentences per GPU (overrides --scaling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gather", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the C1 / C3 / peaky-workload legs")
     ap.add_argument("--eager", action="store_true", help="launch the step kernel by kernel instead of replaying a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    args.repeats = max(args.repeats, 1)
     if args.impl == "reference":
         run_reference(args)
         return
@@ -262,9 +344,10 @@ def main():
     import torch
     import torch.distributed as dist
 
-    from da_transformer_b200 import (_native, dag_best_alignment, dag_logsoftmax_gather_inplace,
+    from da_transformer_b200 import (DagLossFunc, _native, dag_best_alignment, dag_logsoftmax_gather_inplace,
                                      dag_loss, workloads)
     from da_transformer_b200 import dist as ddist
+    from da_transformer_b200.build import PROBE_LIB
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -276,164 +359,222 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     lib = _native.lib()
+    probe = ctypes.CDLL(PROBE_LIB)     # measurement probes: their own library, not the operator path
+    for fn in (probe.dat_probe_mufu, probe.dat_probe_ffma):
+        fn.restype = ctypes.c_int
+        fn.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
     peaks, peak_kind = measured_peaks()
+    ptr, sptr = _native.ptr, _native.stream_ptr
 
-    # ---- data: every rank owns one shard of the global batch
-    # (shard r is drawn from its own generator, seed 20225 + 1000 r, so it is the same
-    # data whatever the number of GPUs and no rank has to generate the other shards)
-    B = args.sentences
+    # ---- data: every rank owns one shard of 512 sentences
+    # (shard r is drawn from its own generator, seed 20225 + 1000 r, so it is the same data whatever
+    # the number of GPUs and no rank has to generate the other shards).  Weak scaling uses the whole
+    # shard; the strong split uses its first 512 / N sentences.
+    B_strong = max(1, GLOBAL_SENTENCES // world)
+    B_weak = GLOBAL_SENTENCES
+    if args.sentences is not None:
+        B_head = args.sentences
+    else:
+        B_head = B_strong if args.scaling == "strong" else B_weak
+    B_gen = args.sentences if args.sentences is not None else B_weak
     gen = workloads.generator(4 + 1000 * rank)
-    shard = workloads.config4(gen=gen, B=B, L=L_GRAPH, V=VOCAB)
-    host = [shard.match_all.pin_memory(), shard.links.pin_memory(),
-            shard.output_length.pin_memory(), shard.target_length.pin_memory()]
-    match = host[0].to(dev).requires_grad_()
-    links = host[1].to(dev).requires_grad_()
-    ol, tl = host[2].to(dev), host[3].to(dev)
-    K = links.shape[2]
-    sweep_exps, total_exps = exp_counts(shard.output_length, shard.target_length, K)
-    gout = (-1.0 / (tl.double() * (B * world))).float()      # d(-(loss/tl).mean())/d loss
+    shard = workloads.config4(gen=gen, B=B_gen, L=L_GRAPH, V=VOCAB)
+    host_all = [shard.match_all, shard.links, shard.output_length, shard.target_length]
+    dev_all = [t.to(dev) for t in host_all]
+    K = dev_all[1].shape[2]
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
-
-    # The alignment and the loss only read match and links, so they are independent: inside the
-    # captured graph the alignment is a parallel branch (a second stream during capture) and its
-    # last, partly filled wave of CTAs overlaps the loss kernels.  Kernel-by-kernel launches keep one
-    # stream (cross-stream tensor reuse made them slower, not faster).
-    align_stream = torch.cuda.Stream(device=dev)
-
-    def local_step(record=None, fork=False):
-        cur = torch.cuda.current_stream(dev)
-        if fork:
-            align_stream.wait_stream(cur)
-            with torch.cuda.stream(align_stream):
-                path = dag_best_alignment(match.detach(), links.detach(), ol, tl)
-        else:
-            path = dag_best_alignment(match.detach(), links.detach(), ol, tl)
-        if record is not None:
-            record[0].record()
-        loss = dag_loss(match, links, ol, tl)
-        if record is not None:
-            record[1].record()
-        gm, gl = torch.autograd.grad(loss, [match, links], grad_outputs=gout)
-        stats = ddist.sentence_stats(loss.detach(), tl)
-        if fork:
-            cur.wait_stream(align_stream)
-        return stats, path, gm, gl
-
-    def step(record=None):
-        stats, path, gm, gl = local_step(record)
-        return ddist.all_reduce_stats(stats), path, gm, gl
-
-    # The ~30 launches of a step (ours and torch's small statistics kernels) cost more host time
-    # than the kernels take on the device, so the rank-local part of the step is captured once
-    # into a CUDA graph and replayed; the all-reduce stays an ordinary NCCL call after it.
-    graph, graph_out, launch_mode = None, None, "eager"
-    if not args.eager:
-        try:
-            side = torch.cuda.Stream(device=dev)
-            side.wait_stream(torch.cuda.current_stream(dev))
-            with torch.cuda.stream(side):
-                for _ in range(3):
-                    local_step()
-            torch.cuda.current_stream(dev).wait_stream(side)
-            torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                graph_out = local_step(fork=True)
-            graph, launch_mode = g, "cuda_graph"
-        except Exception as exc:   # capture not possible here: fall back to kernel-by-kernel launches
-            print(f"[bench] CUDA graph capture failed, running eagerly: {exc}", file=sys.stderr)
-            graph, graph_out = None, None
-            torch.cuda.synchronize()
-
-    def timed_step(record=None):
-        if graph is None:
-            return step(record)
-        graph.replay()
-        return ddist.all_reduce_stats(graph_out[0]), graph_out[1], graph_out[2], graph_out[3]
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- special-function roofline denominator, measured now
+    def max_over_ranks(x):
+        if world > 1:
+            t = torch.tensor([x], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return x
+
+    class Step:
+        """The benchmark step on the first B sentences of the shard: captured once as a CUDA graph
+        (the alignment, independent of the loss, is a parallel branch) and replayed, followed by the
+        NCCL all-reduce of the statistics."""
+
+        def __init__(self, B):
+            self.B = B
+            self.match = dev_all[0][:B].clone().requires_grad_()
+            self.links = dev_all[1][:B].clone().requires_grad_()
+            self.ol, self.tl = dev_all[2][:B].clone(), dev_all[3][:B].clone()
+            self.gout = (-1.0 / (self.tl.double() * (B * world))).float()   # d(-(loss/tl).mean())/d loss
+            self.align_stream = torch.cuda.Stream(device=dev)
+            self.graph, self.out, self.mode = None, None, "eager"
+            if not args.eager:
+                try:
+                    side = torch.cuda.Stream(device=dev)
+                    side.wait_stream(torch.cuda.current_stream(dev))
+                    with torch.cuda.stream(side):
+                        for _ in range(3):
+                            self.local()
+                    torch.cuda.current_stream(dev).wait_stream(side)
+                    torch.cuda.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        self.out = self.local(fork=True)
+                    self.graph, self.mode = g, "cuda_graph"
+                except Exception as exc:   # capture not possible here: kernel-by-kernel launches
+                    print(f"[bench] CUDA graph capture failed, running eagerly: {exc}", file=sys.stderr)
+                    self.graph, self.out = None, None
+                    torch.cuda.synchronize()
+
+        def local(self, fork=False):
+            cur = torch.cuda.current_stream(dev)
+            if fork:
+                self.align_stream.wait_stream(cur)
+                with torch.cuda.stream(self.align_stream):
+                    path = dag_best_alignment(self.match.detach(), self.links.detach(), self.ol, self.tl)
+            else:
+                path = dag_best_alignment(self.match.detach(), self.links.detach(), self.ol, self.tl)
+            loss = dag_loss(self.match, self.links, self.ol, self.tl)
+            gm, gl = torch.autograd.grad(loss, [self.match, self.links], grad_outputs=self.gout)
+            stats = ddist.sentence_stats(loss.detach(), self.tl)
+            if fork:
+                cur.wait_stream(self.align_stream)
+            return stats, path, gm, gl
+
+        def run(self):
+            if self.graph is None:
+                out = self.local()
+            else:
+                self.graph.replay()
+                out = self.out
+            return ddist.all_reduce_stats(out[0])
+
+        def regions(self, steps, repeats, warmup):
+            """`repeats` timed regions of `steps` steps; each bracketed by barrier + synchronize, timed
+            with CUDA events on the launching stream, max over ranks."""
+            for _ in range(warmup):
+                self.run()
+            out = []
+            stats = None
+            for _ in range(repeats):
+                barrier()
+                t0, t1 = ev(), ev()
+                t0.record()
+                for _ in range(steps):
+                    stats = self.run()
+                t1.record()
+                barrier()
+                out.append(max_over_ranks(t0.elapsed_time(t1)))
+            return out, stats
+
+    def summarise(regions_ms, steps, B):
+        med = statistics.median(regions_ms)
+        return {"ms_per_step": med / steps, "ms_per_step_min": min(regions_ms) / steps,
+                "ms_per_step_max": max(regions_ms) / steps, "regions": len(regions_ms),
+                "value": B * world / (med / steps * 1e-3), "sentences_per_gpu": B,
+                "global_sentences": B * world}
+
+    # ---- special-function and fp32-FMA roofline denominators, measured now
     sink = torch.zeros(1, device=dev)
     sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
-    blocks, iters = sm_count * 2, 4096
-    for _ in range(2):
-        _native.check(lib.dat_probe_mufu(iters, blocks, _native.ptr(sink), _native.stream_ptr(dev)), "probe")
-    e0, e1 = ev(), ev()
-    e0.record()
-    _native.check(lib.dat_probe_mufu(iters, blocks, _native.ptr(sink), _native.stream_ptr(dev)), "probe")
-    e1.record()
-    torch.cuda.synchronize()
-    mufu_peak = blocks * 1024 * 8 * iters / (e0.elapsed_time(e1) * 1e-3)   # ex2 / s
 
-    # ---- timed region: device-resident inputs
+    def probe_rate(fn, per_thread):
+        blocks, iters = sm_count * 2, 4096
+        for _ in range(2):
+            fn(iters, blocks, ptr(sink), sptr(dev))
+        e0, e1 = ev(), ev()
+        e0.record()
+        rc = fn(iters, blocks, ptr(sink), sptr(dev))
+        e1.record()
+        torch.cuda.synchronize()
+        if rc != 0:
+            raise RuntimeError("measurement probe failed to launch")
+        return blocks * 1024 * per_thread * iters / (e0.elapsed_time(e1) * 1e-3)
+
+    mufu_peak = probe_rate(probe.dat_probe_mufu, 8)     # ex2 / s
+    ffma_peak = probe_rate(probe.dat_probe_ffma, 16)    # fp32 FMA / s
+
+    # ---- timed regions: device-resident inputs
     uuid = str(torch.cuda.get_device_properties(dev).uuid)
     sampler = ClockSampler(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
     if rank == 0:
         sampler.start()
-    for _ in range(args.warmup):
-        timed_step()
-    marks = [(ev(), ev()) for _ in range(args.steps)]
+    head = Step(B_head)
+    other_B = B_strong if B_head != B_strong else B_weak
+    other = Step(other_B) if (args.sentences is None and other_B != B_head) else None
+    head.regions(1, 1, args.warmup)          # warm-up outside the sampled window
     barrier()
     sampler.begin()
-    t0, t1 = ev(), ev()
-    t0.record()
-    for k in range(args.steps):
-        stats, _, _, _ = timed_step(marks[k])
-    t1.record()
-    barrier()
+    head_regions, stats = head.regions(args.steps, args.repeats, 0)
     sampler.end()
     clocks = sampler.stop() if rank == 0 else None
-    elapsed_ms = t0.elapsed_time(t1)
-    if graph is None:
-        sweep_ms = sum(a.elapsed_time(b) for a, b in marks) / args.steps
-    else:
-        # events cannot be timed inside a replayed graph: time the same forward call, same inputs,
-        # launched directly, once per timed step
+    head_sum = summarise(head_regions, args.steps, B_head)
+    final_stats = stats.cpu().tolist()
+    other_sum = None
+    if other is not None:
+        other_regions, _ = other.regions(args.steps, args.repeats, args.warmup)
+        other_sum = summarise(other_regions, args.steps, other_B)
+    weak_sum = head_sum if B_head == B_weak else other_sum
+    strong_sum = head_sum if B_head == B_strong else other_sum
+    if world == 1 and args.sentences is None:
+        weak_sum = strong_sum = head_sum
+
+    match, links, ol, tl, gout = head.match, head.links, head.ol, head.tl, head.gout
+    B = B_head
+    sweep_exps, total_exps = exp_counts(shard.output_length[:B], shard.target_length[:B], K)
+    ffma_exec, mma_exec = shipped_work(shard.output_length[:B], shard.target_length[:B])
+
+    # ---- the dominant kernel alone: dat_dag_loss_fast launched directly on preallocated buffers,
+    # median of 30 CUDA-event times (nothing is allocated inside the bracket)
+    def time_median(fn, n=30, warm=3):
+        for _ in range(warm):
+            fn()
+        marks = [(ev(), ev()) for _ in range(n)]
+        torch.cuda.synchronize()
         for a, b in marks:
             a.record()
-            dag_loss(match, links, ol, tl)
+            fn()
             b.record()
         torch.cuda.synchronize()
-        sweep_ms = sum(a.elapsed_time(b) for a, b in marks) / args.steps
-    if world > 1:
-        tmax = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(tmax.item())
-    ms_per_step = elapsed_ms / args.steps
-    value = B * world / (ms_per_step * 1e-3)
-    final_stats = stats.cpu().tolist()
+        ts = [a.elapsed_time(b) for a, b in marks]
+        return statistics.median(ts), min(ts), max(ts)
 
-    # ---- per-op breakdown (rank 0, outside the headline region)
-    def time_fn(fn, n=10):
-        for _ in range(3):
-            fn()
-        a, b = ev(), ev()
-        torch.cuda.synchronize()
-        a.record()
-        for _ in range(n):
-            fn()
-        b.record()
-        torch.cuda.synchronize()
-        return a.elapsed_time(b) / n
+    md, ld = match.detach(), links.detach()
+    alpha = torch.empty(B, T_MAX, L_GRAPH, device=dev)
+    beta = torch.empty_like(alpha)
+    offsets = torch.empty(B, 2 * T_MAX + 2, dtype=torch.float64, device=dev)
+    res = torch.empty(B, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    scratch = torch.empty(lib.dat_dag_loss_fast_scratch_bytes(B, T_MAX, L_GRAPH), dtype=torch.uint8, device=dev)
+    flagged = torch.zeros(1, dtype=torch.int32, device=dev)
 
+    def fwd_direct():
+        _native.check(lib.dat_dag_loss_fast(ptr(md), ptr(ld), ptr(ol), ptr(tl), ptr(alpha), ptr(beta), ptr(offsets),
+                                            ptr(res), ptr(status), ptr(scratch), B, T_MAX, L_GRAPH, K, sptr(dev)),
+                      "dag_loss_fast")
+
+    sweep_ms, sweep_ms_min, sweep_ms_max = time_median(fwd_direct)
+    _native.check(lib.dat_dag_loss_fast_flagged(ptr(scratch), ptr(flagged), B, T_MAX, L_GRAPH, sptr(dev)), "flagged")
+    n_flagged = int(flagged.item())
+
+    # ---- per-op breakdown (medians, outside the headline regions)
     breakdown = {}
     if rank == 0:
-        breakdown["best_alignment_ms"] = time_fn(lambda: dag_best_alignment(match.detach(), links.detach(), ol, tl))
-        breakdown["loss_fwd_alpha_beta_ms"] = time_fn(lambda: dag_loss(match, links, ol, tl))
-        with torch.no_grad():
-            breakdown["loss_fwd_alpha_only_ms"] = time_fn(lambda: dag_loss(match, links, ol, tl))
+        breakdown["best_alignment_ms"] = time_median(lambda: dag_best_alignment(md, ld, ol, tl), 15)[0]
+        breakdown["loss_fwd_alpha_beta_ms"] = time_median(lambda: dag_loss(match, links, ol, tl), 15)[0]
+        breakdown["loss_fwd_no_grad_ms"] = time_median(lambda: dag_loss(md, ld, ol, tl), 15)[0]
         loss_keep = dag_loss(match, links, ol, tl)
-        breakdown["loss_bwd_ms"] = time_fn(lambda: torch.autograd.grad(loss_keep, [match, links], grad_outputs=gout,
-                                                                       retain_graph=True))
+        breakdown["loss_bwd_ms"] = time_median(
+            lambda: torch.autograd.grad(loss_keep, [match, links], grad_outputs=gout, retain_graph=True), 15)[0]
         fb = breakdown["loss_fwd_alpha_beta_ms"] + breakdown["loss_bwd_ms"]
         breakdown["dag_loss_fwd_bwd_only_sentences_per_s"] = B / (fb * 1e-3)
+        breakdown["flagged_sentences"] = n_flagged
+        del loss_keep
 
     # ---- end to end through the public API: host inputs in, statistics out, every step
+    host = [t[:B].contiguous().pin_memory() for t in host_all]
     h2d = sum(t.numel() * t.element_size() for t in host)
     d2h = 4 * 8
     stats_host = torch.empty(4, dtype=torch.float64).pin_memory()
@@ -479,56 +620,70 @@ def main():
         torch.cuda.current_stream().synchronize()      # the last statistics have reached the host
 
     e2e_run(3)
-    barrier()
-    t0, t1 = ev(), ev()
-    t0.record()
-    e2e_run(args.steps)
-    t1.record()
-    barrier()
-    e2e_ms = t0.elapsed_time(t1)
-    if world > 1:
-        tmax = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        e2e_ms = float(tmax.item())
+    e2e_regions = []
+    for _ in range(min(args.repeats, 5)):
+        barrier()
+        t0, t1 = ev(), ev()
+        t0.record()
+        e2e_run(args.steps)
+        t1.record()
+        barrier()
+        e2e_regions.append(max_over_ranks(t0.elapsed_time(t1)))
+    e2e_ms = statistics.median(e2e_regions)
     e2e_value = B * world / (e2e_ms / args.steps * 1e-3)
+    del bufs, host
 
-    # ---- logsoftmax_gather on the C2 shape (rank-local), HBM roofline
+    # ---- logsoftmax_gather on the C2 shapes (rank 0), HBM roofline
     gather = None
     if rank == 0 and not args.no_gather:
-        Bg, Lg, Vg, Sg = 32, 1024, 32000, 128
-        g2 = torch.Generator(device=dev)
-        g2.manual_seed(workloads.BASE_SEED + 2)
-        base = (torch.randn(Bg, Lg, Vg, device=dev, generator=g2) * 2.0).to(torch.bfloat16)
-        idx = torch.randint(0, Vg, (Bg, Lg, Sg), device=dev, generator=g2)
-        gsel = torch.randn(Bg, Lg, Sg, device=dev, generator=g2)
-        fwd_ms, bwd_ms = [], []
-        for it in range(8):
-            x = base.clone().requires_grad_()
-            work = x.clone()
-            a, b, c = ev(), ev(), ev()
-            a.record()
-            _, sel = dag_logsoftmax_gather_inplace(work, idx)
-            b.record()
-            sel.backward(gsel)
-            c.record()
-            torch.cuda.synchronize()
-            if it >= 3:
-                fwd_ms.append(a.elapsed_time(b))
-                bwd_ms.append(b.elapsed_time(c))
-            del x, work, sel
-        e = 2
-        fwd_bytes = Bg * Lg * Vg * e + 4 * Bg * Lg * Sg + 8 * Bg * Lg * Sg
-        bwd_bytes = 2 * Bg * Lg * Vg * e + 4 * Bg * Lg * Sg + 8 * Bg * Lg * Sg
-        f, bw = statistics.median(fwd_ms), statistics.median(bwd_ms)
-        gather = {
-            "workload": f"C2: logits [{Bg},{Lg},{Vg}] bf16 N(0,2), select_idx [{Bg},{Lg},{Sg}] int64",
-            "fwd_ms": f, "bwd_ms": bw,
-            "fwd_gbs": fwd_bytes / f / 1e6, "bwd_gbs": bwd_bytes / bw / 1e6,
-            "fwd_bwd_gbs": (fwd_bytes + bwd_bytes) / (f + bw) / 1e6,
-            "peak_gbs": peaks["hbm_gbs"], "peak_kind": peak_kind,
-            "frac": (fwd_bytes + bwd_bytes) / (f + bw) / 1e6 / peaks["hbm_gbs"],
-        }
-        del base, idx, gsel
+        Bg, Lg, Sg = 32, 1024, 128
+        cases = []
+        for dt in (torch.bfloat16, torch.float16):
+            for Vg in (32000, 50000, 64000):
+                g2 = torch.Generator(device=dev)
+                g2.manual_seed(workloads.BASE_SEED + 2)
+                base = torch.empty(Bg, Lg, Vg, dtype=dt, device=dev)
+                for b in range(Bg):
+                    base[b] = (torch.randn(Lg, Vg, device=dev, generator=g2) * 2.0).to(dt)
+                idx = torch.randint(0, Vg, (Bg, Lg, Sg), device=dev, generator=g2)
+                gsel = torch.randn(Bg, Lg, Sg, device=dev, generator=g2)
+                fwd_ms, bwd_ms = [], []
+                for it in range(8):
+                    x = base.clone().requires_grad_()
+                    work = x.clone()
+                    a, b_, c = ev(), ev(), ev()
+                    a.record()
+                    _, sel = dag_logsoftmax_gather_inplace(work, idx)
+                    b_.record()
+                    sel.backward(gsel)
+                    c.record()
+                    torch.cuda.synchronize()
+                    if it >= 3:
+                        fwd_ms.append(a.elapsed_time(b_))
+                        bwd_ms.append(b_.elapsed_time(c))
+                    del x, work, sel
+                e = 2
+                fwd_bytes = Bg * Lg * Vg * e + 4 * Bg * Lg * Sg + 8 * Bg * Lg * Sg
+                bwd_bytes = 2 * Bg * Lg * Vg * e + 4 * Bg * Lg * Sg + 8 * Bg * Lg * Sg
+                f, bw = statistics.median(fwd_ms), statistics.median(bwd_ms)
+                cases.append({
+                    "dtype": str(dt).replace("torch.", ""), "vocab": Vg,
+                    "fwd_ms": f, "bwd_ms": bw, "fwd_gbs": fwd_bytes / f / 1e6, "bwd_gbs": bwd_bytes / bw / 1e6,
+                    "fwd_bwd_gbs": (fwd_bytes + bwd_bytes) / (f + bw) / 1e6,
+                    "frac": (fwd_bytes + bwd_bytes) / (f + bw) / 1e6 / peaks["hbm_gbs"],
+                    "frac_of_nominal_8000": (fwd_bytes + bwd_bytes) / (f + bw) / 1e6 / 8000.0,
+                    "algorithmic_bytes": fwd_bytes + bwd_bytes,
+                })
+                del base, idx, gsel
+                torch.cuda.empty_cache()
+        gather = {"workload": f"C2: logits [{Bg},{Lg},V] N(0,2), select_idx [{Bg},{Lg},{Sg}] int64, fwd+bwd",
+                  "peak_gbs": peaks["hbm_gbs"], "peak_kind": peak_kind, "cases": cases}
+
+    # ---- the other configurations' step times and the peaky (trained-like) workload, rank 0
+    configs = {}
+    if rank == 0 and not args.no_extra:
+        configs = extra_legs(torch, dev, ev, workloads, dag_loss, dag_best_alignment, dag_logsoftmax_gather_inplace,
+                             DagLossFunc, lib, _native, time_median)
 
     if rank != 0:
         if world > 1:
@@ -536,23 +691,31 @@ def main():
         return
 
     sweep_rate = sweep_exps / (sweep_ms * 1e-3)
+    scaling = "strong" if (args.sentences is None and args.scaling == "strong") else "weak"
     out = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "metric": METRIC, "value": head_sum["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": head_sum["ms_per_step"],
+        "ms_per_step_min": head_sum["ms_per_step_min"], "ms_per_step_max": head_sum["ms_per_step_max"],
+        "timed_regions": head_sum["regions"],
+        "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {
             "workload": ("C4: per GPU %d sentences, L=512 (=output_length), target_length~U{32..64}, T=64, "
                          "fp32 links [B,512,511] + fp32 match [B,64,512]; step = dag_best_alignment + dag_loss "
-                         "fwd (alpha+beta) + bwd + scalar all-reduce") % B,
+                         "fwd (alpha+beta) + bwd + statistics + scalar all-reduce") % B,
             "sentences_per_gpu": B, "global_sentences": B * world, "parallelism": f"dp{world}",
-            "l2": "inputs (600 MB per GPU) exceed L2; no flush between steps",
-            "launch": launch_mode,
+            "l2": ("inputs (%.0f MB per GPU) exceed L2; no flush between steps" % (h2d / 1e6)) if h2d > 126e6 * 1.5
+                  else ("inputs are %.0f MB per GPU, less than L2 holds: the links stay L2-resident between steps, "
+                        "as they would after the model's forward pass wrote them" % (h2d / 1e6)),
+            "launch": head.mode,
+            "timing": f"{args.repeats} regions of {args.steps} steps, median region / steps",
         },
+        "weak": weak_sum, "strong": strong_sum,
         "clocks": clocks,
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "regions": len(e2e_regions)},
         # per step: alignment (1: strip kernel), loss forward (4: order, strip sweep, check, exact
         # fallback), loss backward (3: grad_match, product-form grad_links, exact fallback), statistics (1)
-        "gpu_launches": 9 * args.steps,
+        "gpu_launches": 9 * args.steps * args.repeats,
         "roofline": {
             "kernel": ("dag_loss forward = dag_strip_sweep_kernel (alpha and beta recursions, one CTA each, "
                        "exp(links) blocks held in registers) with its order, check and fallback launches"),
@@ -561,25 +724,149 @@ def main():
             # dram__bytes_read+write of dag_strip_sweep_kernel from the ncu capture summarised in
             # profiles/dag_strip_sweep_c4_148sent.md (108.7 MB for 148 sentences), scaled by sentences
             "traffic": 108.7e6 / 148 * B,
-            "peak_kind": "measured on this device by dat_probe_mufu just before the timed region",
+            "peak_kind": "measured on this device by the ex2 probe just before the timed regions",
             "nominal_peak": 16 * sm_count * peaks.get("sm_max_mhz", 1965.0) * 1e6 / 1e9,
             "algorithmic_exps_per_launch": sweep_exps, "kernel_ms": sweep_ms,
-            "step_frac_all_kernels": (total_exps / (ms_per_step * 1e-3)) / mufu_peak,
+            "kernel_ms_min": sweep_ms_min, "kernel_ms_max": sweep_ms_max,
+            "kernel_ms_how": "median of 30 direct dat_dag_loss_fast launches on preallocated buffers",
+            "step_frac_all_kernels": (total_exps / (head_sum["ms_per_step"] * 1e-3)) / mufu_peak,
+        },
+        "roofline_shipped": {
+            "what": ("work dag_strip_sweep_kernel executes per launch: 32x32 blocks inside a 128-vertex group as "
+                     "fp32 FMAs, all other blocks as 3xTF32 tensor-core products (mma.sync m16n8k8)"),
+            "ffma_executed": ffma_exec, "ffma_rate_tfma_s": ffma_exec / (sweep_ms * 1e-3) / 1e12,
+            "ffma_peak_tfma_s": ffma_peak / 1e12, "ffma_frac": ffma_exec / (sweep_ms * 1e-3) / ffma_peak,
+            "tf32_fma_executed": mma_exec, "tf32_rate_tfma_s": mma_exec / (sweep_ms * 1e-3) / 1e12,
+            "tf32_nominal_peak_tfma_s": 550.0, "tf32_frac_of_nominal": mma_exec / (sweep_ms * 1e-3) / 550e12,
+            "all_terms_as_fma_frac": (sweep_exps / (sweep_ms * 1e-3)) / ffma_peak,
+            "ffma_peak_kind": "measured on this device by the FMA probe",
         },
         "breakdown": breakdown,
         "gather": gather,
-        "loss_check": {"mean_nll_per_token": -final_stats[0] / final_stats[2], "invalid": final_stats[3]},
+        "configs": configs,
+        "loss_check": {"mean_nll_per_token": -final_stats[0] / final_stats[2], "invalid": final_stats[3],
+                       "flagged_sentences": n_flagged},
     }
     if gather is not None:
-        out["roofline_gather"] = {"bound": "hbm", "achieved": gather["fwd_bwd_gbs"], "peak": peaks["hbm_gbs"],
-                                  "unit": "GB/s", "frac": gather["frac"], "traffic": None,
-                                  "peak_kind": peak_kind}
+        c0 = gather["cases"][0]
+        out["roofline_gather"] = {"bound": "hbm", "achieved": c0["fwd_bwd_gbs"], "peak": peaks["hbm_gbs"],
+                                  "unit": "GB/s", "frac": c0["frac"],
+                                  "case": f"{c0['dtype']} V={c0['vocab']}",
+                                  # dram__bytes_read+write of lsg_fwd_kernel + lsg_bwd_kernel from the ncu
+                                  # capture summarised in profiles/lsg_c2_bf16_v32000.md
+                                  "traffic": GATHER_TRAFFIC_BYTES,
+                                  "algorithmic_bytes": c0["algorithmic_bytes"], "peak_kind": peak_kind}
     if world == 1 and not args.no_cpu_baseline:
         out["cpu_baseline"] = cpu_baseline()
+        out["cpu_baseline_torch"] = cpu_baseline_torch()
         out["reference_cuda"] = reference_cuda_baseline(match, links, ol, tl, gout)
     print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
+
+
+# dram bytes (read + write) of one forward + one backward launch of the gather on C2 bf16 V=32000
+# (profiles/lsg_c2_bf16_v32000.md); None until that capture exists for the current kernels
+GATHER_TRAFFIC_BYTES = None
+
+
+def extra_legs(torch, dev, ev, workloads, dag_loss, dag_best_alignment, dag_logsoftmax_gather_inplace, DagLossFunc,
+               lib, _native, time_median):
+    """Step times of the configurations that are not the headline: C1 (the translation-shaped step with
+    fp16 logits, gather included), C3 (long sequences) and a peaky, trained-like C4 variant."""
+    from da_transformer_b200 import last_status
+
+    out = {}
+    # C1: B=64 ragged, fp16 logits [64, L<=512, 42000]; step = gather (no grad) + alignment + gather + loss
+    # forward/backward + gather backward
+    b = workloads.config1(with_logits=False)
+    Bc, T, L = b.match_all.shape
+    g = torch.Generator(device=dev)
+    g.manual_seed(workloads.BASE_SEED + 1)
+    logits = torch.empty(Bc, L, 42000, dtype=torch.float16, device=dev)
+    for i in range(Bc):
+        logits[i] = (torch.randn(L, 42000, device=dev, generator=g) * 2.0).to(torch.float16)
+    bd = b.to(dev)
+    sel_idx = bd.select_idx
+    links = bd.links.clone().requires_grad_()
+    leaf = logits.requires_grad_()
+
+    def c1_step():
+        with torch.no_grad():
+            _, sel = dag_logsoftmax_gather_inplace(leaf.detach(), sel_idx)
+            dag_best_alignment(sel.transpose(1, 2), bd.links, bd.output_length, bd.target_length)
+        work = leaf.clone()       # the op overwrites its input with the gradient; part of the reference's step too
+        _, sel = dag_logsoftmax_gather_inplace(work, sel_idx)
+        loss = dag_loss(sel.transpose(1, 2), links, bd.output_length, bd.target_length)
+        torch.autograd.grad(-(loss / bd.target_length).mean(), [leaf, links])
+
+    def c1_dag_only():
+        m = bd_match.requires_grad_()
+        dag_best_alignment(m.detach(), bd.links, bd.output_length, bd.target_length)
+        loss = dag_loss(m, links, bd.output_length, bd.target_length)
+        torch.autograd.grad(loss.sum(), [m, links])
+
+    with torch.no_grad():
+        _, sel0 = dag_logsoftmax_gather_inplace(leaf.detach(), sel_idx)
+    bd_match = sel0.transpose(1, 2).contiguous()
+    med, lo, hi = time_median(c1_step, 10)
+    med_d, _, _ = time_median(c1_dag_only, 10)
+    out["C1"] = {"workload": f"B={Bc}, L={L}, T={T}, V=42000, fp16 logits: gather(no grad) + alignment + gather + "
+                             f"dag_loss fwd+bwd + gather bwd (includes one clone of the logits)",
+                 "ms_per_step": med, "ms_min": lo, "ms_max": hi, "sentences_per_s": Bc / (med * 1e-3),
+                 "dag_ops_only_ms": med_d}
+    del logits, leaf, sel0, bd_match, links
+    torch.cuda.empty_cache()
+
+    # C3: B=16, L=1024, T<=256
+    b = workloads.config3().to(dev)
+    m = b.match_all.clone().requires_grad_()
+    l = b.links.clone().requires_grad_()
+
+    def c3_step():
+        dag_best_alignment(m.detach(), l.detach(), b.output_length, b.target_length)
+        loss = dag_loss(m, l, b.output_length, b.target_length)
+        torch.autograd.grad(loss.sum(), [m, l])
+
+    med, lo, hi = time_median(c3_step, 10)
+    out["C3"] = {"workload": f"B={b.match_all.shape[0]}, L=1024, T={b.match_all.shape[1]}: alignment + dag_loss fwd+bwd",
+                 "ms_per_step": med, "ms_min": lo, "ms_max": hi,
+                 "sentences_per_s": b.match_all.shape[0] / (med * 1e-3)}
+    del m, l, b
+    torch.cuda.empty_cache()
+
+    # Peaky, trained-like C4 variant: link scores x 8, one dominant vertex per target token
+    pk = workloads.config4_peaky().to(dev)
+    m = pk.match_all.clone().requires_grad_()
+    l = pk.links.clone().requires_grad_()
+    Bp = m.shape[0]
+    last_status()
+
+    def pk_step():
+        dag_best_alignment(m.detach(), l.detach(), pk.output_length, pk.target_length)
+        loss = dag_loss(m, l, pk.output_length, pk.target_length)
+        torch.autograd.grad(loss.sum(), [m, l])
+
+    med, lo, hi = time_median(pk_step, 10)
+    K = l.shape[2]
+    T, L = m.shape[1], m.shape[2]
+    alpha = torch.empty(Bp, T, L, device=dev)
+    beta = torch.empty_like(alpha)
+    offsets = torch.empty(Bp, 2 * T + 2, dtype=torch.float64, device=dev)
+    res = torch.empty(Bp, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    scratch = torch.empty(lib.dat_dag_loss_fast_scratch_bytes(Bp, T, L), dtype=torch.uint8, device=dev)
+    flagged = torch.zeros(1, dtype=torch.int32, device=dev)
+    p, s = _native.ptr, _native.stream_ptr
+    _native.check(lib.dat_dag_loss_fast(p(m.detach()), p(l.detach()), p(pk.output_length), p(pk.target_length), p(alpha),
+                                        p(beta), p(offsets), p(res), p(status), p(scratch), Bp, T, L, K, s(dev)), "fast")
+    _native.check(lib.dat_dag_loss_fast_flagged(p(scratch), p(flagged), Bp, T, L, s(dev)), "flagged")
+    out["C4_peaky"] = {"workload": f"B={Bp}, L=512, T=64, link scores x 8 and one dominant vertex per target token "
+                                   f"(trained-like): alignment + dag_loss fwd+bwd",
+                       "ms_per_step": med, "ms_min": lo, "ms_max": hi, "sentences_per_s": Bp / (med * 1e-3),
+                       "flagged_sentences": int(flagged.item()), "finite_losses": int(torch.isfinite(res).sum().item())}
+    last_status()
+    return out
 
 
 if __name__ == "__main__":

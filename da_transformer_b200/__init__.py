@@ -16,6 +16,8 @@ from .dag_loss import (  # noqa: F401
     logsoftmax_gather,
 )
 
+from .criterion_glue import dag_loss_mean, dag_match, glat_alignment  # noqa: F401
+from .graph_ops import dag_links_from_heads, dag_node_passing_prob, dag_viterbi_decode  # noqa: F401
 from .torch_twins import (  # noqa: F401
     torch_dag_best_alignment,
     torch_dag_logsoftmax_gather_inplace,

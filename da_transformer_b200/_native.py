@@ -20,8 +20,11 @@ EXPORTS = (
     "dat_version", "dat_last_error", "dat_status_string", "dat_dag_loss_offsets_bytes",
     "dat_dag_best_alignment_workspace_bytes", "dat_logsoftmax_gather",
     "dat_logsoftmax_gather_backward", "dat_dag_loss", "dat_dag_loss_backward",
-    "dat_dag_best_alignment", "dat_probe_mufu", "dat_dag_loss_static", "dat_sentence_stats",
+    "dat_dag_best_alignment", "dat_dag_loss_static", "dat_sentence_stats",
     "dat_dag_loss_fast", "dat_dag_loss_fast_scratch_bytes", "dat_dag_loss_backward_fast",
+    "dat_logsoftmax_gather_fused", "dat_logsoftmax_gather_backward_fused", "dat_sentence_mean",
+    "dat_links_from_heads", "dat_links_from_heads_backward", "dat_node_passing_prob",
+    "dat_viterbi_decode", "dat_viterbi_decode_workspace_bytes", "dat_dag_loss_fast_flagged",
 )
 
 _lib = None
@@ -56,12 +59,30 @@ def _declare(lib):
     lib.dat_dag_loss_fast_scratch_bytes.argtypes = [_i32, _i32, _i32]
     lib.dat_dag_loss_fast.restype = _i32
     lib.dat_dag_loss_fast.argtypes = [_vp] * 10 + [_i32] * 4 + [_vp]
+    lib.dat_dag_loss_fast_flagged.restype = _i32
+    lib.dat_dag_loss_fast_flagged.argtypes = [_vp, _vp, _i32, _i32, _i32, _vp]
     lib.dat_dag_loss_backward_fast.restype = _i32
     lib.dat_dag_loss_backward_fast.argtypes = [_vp] * 11 + [_i32] * 4 + [_vp]
-    lib.dat_probe_mufu.restype = _i32
-    lib.dat_probe_mufu.argtypes = [_i32, _i32, _vp, _vp]
     lib.dat_sentence_stats.restype = _i32
     lib.dat_sentence_stats.argtypes = [_vp, _vp, _vp, _i32, _vp]
+    lib.dat_sentence_mean.restype = _i32
+    lib.dat_sentence_mean.argtypes = [_vp, _vp, _vp, _vp, _vp, _i32, _vp]
+    lib.dat_links_from_heads.restype = _i32
+    lib.dat_links_from_heads.argtypes = [_vp] * 6 + [_i32] * 4 + [_vp]
+    lib.dat_links_from_heads_backward.restype = _i32
+    lib.dat_links_from_heads_backward.argtypes = [_vp] * 9 + [_i32] * 4 + [_vp]
+    lib.dat_node_passing_prob.restype = _i32
+    lib.dat_node_passing_prob.argtypes = [_vp, _vp, _i32, _i32, _vp]
+    lib.dat_viterbi_decode_workspace_bytes.restype = ctypes.c_size_t
+    lib.dat_viterbi_decode_workspace_bytes.argtypes = [_i32, _i32, _i32]
+    lib.dat_viterbi_decode.restype = _i32
+    lib.dat_viterbi_decode.argtypes = [_vp] * 10 + [_i32] * 4 + [ctypes.c_float, _i64, _vp]
+    lib.dat_logsoftmax_gather_fused.restype = _i32
+    lib.dat_logsoftmax_gather_fused.argtypes = [_vp, _i32, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _i64,
+                                                _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]
+    lib.dat_logsoftmax_gather_backward_fused.restype = _i32
+    lib.dat_logsoftmax_gather_backward_fused.argtypes = [_vp, _i32, _vp, _i64, _i64, _i64, _vp, _i64,
+                                                         _i64, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _vp]
 
 
 def lib():

@@ -570,6 +570,22 @@ dag_fast_grad_links_kernel(const float *__restrict__ grad_out, const float *__re
     }
 }
 
+// number of sentences the forward handed to the exact kernels
+__global__ void dag_fast_flagged_kernel(const int *__restrict__ flag, int32_t *__restrict__ count, int B) {
+    int n = 0;
+    for (int b = threadIdx.x; b < B; b += blockDim.x) n += flag[b] != 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
+    __shared__ int part[32];
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = n;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); w++) t += part[w];
+        *count = t;
+    }
+}
+
 // defined in dag_sweep.cu
 int launch_exact_sweeps(const float *match_all, const float *links, const int64_t *output_length,
                         const int64_t *target_length, const int *select, float *alpha, float *beta,
@@ -640,6 +656,16 @@ int dat_dag_loss_backward_fast(const float *grad_output, const float *alpha, con
                                    "dat_dag_loss_backward_fast(exact)");
 }
 
+int dat_dag_loss_fast_flagged(const void *scratch, int32_t *count, int bsz, int tarlen, int prelen,
+                              void *stream) {
+    using namespace dat;
+    DAT_REQUIRE(scratch && count && bsz >= 1 && tarlen >= 1 && prelen >= 1, DAT_ERR_BAD_ARG,
+                "dat_dag_loss_fast_flagged: bad argument");
+    const FastScratch sc = carve_fast(const_cast<void *>(scratch), bsz, tarlen, prelen);
+    dag_fast_flagged_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(sc.flag, count, bsz);
+    return check_launch("dat_dag_loss_fast_flagged");
+}
+
 size_t dat_dag_loss_fast_scratch_bytes(int bsz, int tarlen, int prelen) {
     if (bsz <= 0 || tarlen <= 0 || prelen <= 0) return 0;
     // the square exp(links) matrix is only needed when the tiled sweep runs on the current device
@@ -660,8 +686,10 @@ int dat_dag_loss_fast(const float *match_all, const float *links, const int64_t 
     DAT_REQUIRE(match_all && links && output_length && target_length && alpha && beta && offsets &&
                     loss && scratch,
                 DAT_ERR_BAD_ARG, "dat_dag_loss_fast: null pointer");
-    DAT_REQUIRE(prelen <= 2 * kSweepThreads, DAT_ERR_UNSUPPORTED,
-                "dat_dag_loss_fast: prelen=%d exceeds %d", prelen, 2 * kSweepThreads);
+    DAT_REQUIRE(prelen <= kMaxPrelen, DAT_ERR_UNSUPPORTED,
+                "dat_dag_loss_fast: prelen=%d exceeds %d", prelen, kMaxPrelen);
+    DAT_REQUIRE(tarlen <= kMaxTarlenGrad, DAT_ERR_UNSUPPORTED,
+                "dat_dag_loss_fast: tarlen=%d exceeds %d (limit of the backward)", tarlen, kMaxTarlenGrad);
     DeviceInfo di;
     if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -8,7 +8,7 @@
 // term that reaches the MUFU is O(10) in magnitude however long the sentence is.
 // Both outputs are written completely, zeros included, so the caller may pass
 // uninitialised buffers.
-#include "dat_common.cuh"
+#include "dag_tiles.cuh"
 
 namespace dat {
 
@@ -156,7 +156,12 @@ int launch_exact_grad_links(const float *grad_output, const float *alpha, const 
                             const int64_t *target_length, float *grad_links, const int *select, int bsz,
                             int tarlen, int prelen, int translen, cudaStream_t st, const char *who) {
     const size_t smem = (size_t)tarlen * kGlRows * sizeof(float);
-    DAT_REQUIRE(smem <= 48 * 1024, DAT_ERR_UNSUPPORTED, "%s: tarlen=%d too large", who, tarlen);
+    DAT_REQUIRE(tarlen <= kMaxTarlenGrad, DAT_ERR_UNSUPPORTED, "%s: tarlen=%d exceeds %d", who, tarlen,
+                kMaxTarlenGrad);
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(dag_grad_links_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+        return check_launch(who);
     dim3 grid((prelen + kGlRows - 1) / kGlRows, bsz);
     dag_grad_links_kernel<<<grid, kGlThreads, smem, st>>>(grad_output, alpha, beta, offsets, links,
                                                          output_length, target_length, grad_links, select,

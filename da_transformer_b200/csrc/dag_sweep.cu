@@ -82,9 +82,9 @@ __device__ void alpha_sweep(const float *__restrict__ match, const float *__rest
         const float *prev = (t & 1) ? sm.row0 : sm.row1;  // row of step t-1
         float *cur = (t & 1) ? sm.row1 : sm.row0;
         // match of this thread's merge columns, requested early
-        float mt[2];
+        float mt[kMergeCols];
 #pragma unroll
-        for (int q = 0; q < 2; q++) {
+        for (int q = 0; q < kMergeCols; q++) {
             int c = tid + q * kSweepThreads;
             mt[q] = (c < W) ? ld_early(match + (size_t)t * L + t + c) : 0.f;
         }
@@ -163,7 +163,7 @@ __device__ void alpha_sweep(const float *__restrict__ match, const float *__rest
         const float delta = delta_s;
         float vmax = kNegBig;
 #pragma unroll
-        for (int q = 0; q < 2; q++) {
+        for (int q = 0; q < kMergeCols; q++) {
             const int c = tid + q * kSweepThreads;
             if (c < W) {
                 const int cb = c >> 5, ln = c & 31;
@@ -399,8 +399,10 @@ int dat_dag_loss(const float *match_all, const float *links, const int64_t *outp
                 DAT_ERR_BAD_ARG, "dat_dag_loss: null pointer");
     DAT_REQUIRE(!require_gradient || beta, DAT_ERR_BAD_ARG,
                 "dat_dag_loss: beta workspace required when require_gradient");
-    DAT_REQUIRE(prelen <= 2 * kSweepThreads, DAT_ERR_UNSUPPORTED,
-                "dat_dag_loss: prelen=%d exceeds %d", prelen, 2 * kSweepThreads);
+    DAT_REQUIRE(prelen <= kMaxPrelen, DAT_ERR_UNSUPPORTED,
+                "dat_dag_loss: prelen=%d exceeds %d", prelen, kMaxPrelen);
+    DAT_REQUIRE(!require_gradient || tarlen <= kMaxTarlenGrad, DAT_ERR_UNSUPPORTED,
+                "dat_dag_loss: tarlen=%d exceeds %d (limit of the backward)", tarlen, kMaxTarlenGrad);
     DAT_REQUIRE((long long)prelen * translen < (1ll << 31), DAT_ERR_UNSUPPORTED,
                 "dat_dag_loss: prelen*translen too large");
     return launch_exact_sweeps(match_all, links, output_length, target_length, nullptr, alpha, beta,
@@ -481,8 +483,8 @@ extern "C" int dat_dag_loss_static(const float *match_all, const float *links,
                 "floats (or bsz*(2*tarlen+2) = %zu exceeds %zu); use dat_dag_loss with caller-provided "
                 "workspaces for larger batches",
                 need_rows, kStaticRowFloats, need_offs, kStaticOffsetDoubles);
-    DAT_REQUIRE(prelen <= 2 * kSweepThreads, DAT_ERR_UNSUPPORTED,
-                "dat_dag_loss_static: prelen=%d exceeds %d", prelen, 2 * kSweepThreads);
+    DAT_REQUIRE(prelen <= kMaxPrelen, DAT_ERR_UNSUPPORTED,
+                "dat_dag_loss_static: prelen=%d exceeds %d", prelen, kMaxPrelen);
     DAT_REQUIRE((long long)prelen * translen < (1ll << 31), DAT_ERR_UNSUPPORTED,
                 "dat_dag_loss_static: prelen*translen too large");
     DeviceInfo di;

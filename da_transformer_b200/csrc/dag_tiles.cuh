@@ -19,6 +19,11 @@ namespace dat {
 constexpr int kSweepThreads = 512;
 constexpr int kSweepWarps = kSweepThreads / 32;
 constexpr int kChunk = 8;
+// Window columns one thread of the alpha sweep finalises per step; bounds the graph length.
+constexpr int kMergeCols = 4;
+constexpr int kMaxPrelen = kMergeCols * kSweepThreads;   // 2048 vertices
+// The exact grad_links kernel stages tarlen x 8 floats in shared memory (opt-in limit 227 KB).
+constexpr int kMaxTarlenGrad = 7168;
 
 __host__ __device__ inline bool lengths_valid(long long ol, long long tl, int T, int L) {
     return tl >= 2 && ol >= 2 && ol >= tl && ol <= L && tl <= T;

@@ -1,0 +1,258 @@
+// Decode-side dynamic programmes over the SQUARE transition matrix (links[b,i,j] = log P(v_i -> v_j),
+// -inf for j <= i), for sm_100a.  The training ops work on the band layout; decoding restores the
+// square one first (restore_valid_links, fs_plugins/models/glat_decomposed_with_link.py:337-349).
+//
+//   dat_node_passing_prob: the probability that a path from vertex 0 passes through each vertex
+//     (GlatDecomposedLink._analyze_graph, glat_decomposed_with_link.py:559-569).  The reference sums,
+//     over path lengths s = 0..L-1, the probability of sitting on vertex j after exactly s
+//     transitions (L-1 log-sum-exp products over the whole [L,L] matrix).  Edges only go left to
+//     right, so that sum is the solution of the triangular system
+//         pass[0] = 1,   pass[j] = sum_{i<j} pass[i] * exp(links[i][j]),
+//     one sweep over the matrix.
+//   dat_viterbi_decode: GlatDecomposedLink.inference_viterbi (glat_decomposed_with_link.py:720-777):
+//     max-plus recursion over the number of emitted tokens with back-pointers, the length-normalised
+//     choice of the best length, the back-trace and the collapse of repeated / pad tokens, all on the
+//     device (the reference back-traces in Python lists on the host).
+// One CTA per sentence; the matrix of a sentence (<= 4 MB) is served by L2 after its first read.
+#include <climits>
+
+#include "dat_common.cuh"
+
+namespace dat {
+
+constexpr int kDecThreads = 512;
+constexpr int kDecWarps = kDecThreads / 32;
+
+__global__ void __launch_bounds__(256)
+node_pass_kernel(const float *__restrict__ links_all, float *__restrict__ pass_all, int L) {
+    extern __shared__ float nsm[];
+    float *pass = nsm;              // [Lp]
+    float *part = nsm + ((L + 31) & ~31);   // [8][32]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float *lk = links_all + (size_t)blockIdx.x * L * L;
+    const int nblk = (L + 31) >> 5;
+    for (int jb = 0; jb < nblk; jb++) {
+        const int j = 32 * jb + lane;
+        // what the finished vertices (i < 32 jb) send into this block of 32 columns
+        float acc = 0.f;
+        if (j < L)
+            for (int i = warp; i < 32 * jb; i += 8) acc = fmaf(pass[i], ex2(__ldg(lk + (size_t)i * L + j) * kLog2e), acc);
+        part[warp * 32 + lane] = acc;
+        __syncthreads();
+        if (warp == 0) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; w++) v += part[w * 32 + lane];
+            if (jb == 0 && lane == 0) v = 1.f;
+            // the block's own triangle, column by column: lane c receives pass[r] * E[r][c] from every r < c
+            float e[32];
+#pragma unroll
+            for (int r = 0; r < 32; r++) {
+                const int i = 32 * jb + r;
+                e[r] = (r < lane && j < L) ? ex2(__ldg(lk + (size_t)i * L + j) * kLog2e) : 0.f;
+            }
+#pragma unroll
+            for (int r = 0; r < 31; r++) {
+                const float pr = __shfl_sync(0xffffffffu, v, r);   // final: every r' < r has been added
+                v = fmaf(pr, e[r], v);
+            }
+            if (j < L) {
+                pass[j] = v;
+                pass_all[(size_t)blockIdx.x * L + j] = v;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// Candidate order of torch.max along a dimension: larger value first, then the smaller index.
+__device__ __forceinline__ void vit_better(float &bv, int &bi, float v, int i) {
+    if (v > bv || (v == bv && i < bi)) {
+        bv = v;
+        bi = i;
+    }
+}
+
+__global__ void __launch_bounds__(kDecThreads)
+viterbi_decode_kernel(const float *__restrict__ links_all, const float *__restrict__ logits_all,
+                      const int64_t *__restrict__ tokens_all, const int64_t *__restrict__ output_length,
+                      int32_t *__restrict__ trace_all, int64_t *__restrict__ out_tokens,
+                      int64_t *__restrict__ out_length, int64_t *__restrict__ out_vertices,
+                      float *__restrict__ out_score, int32_t *__restrict__ status, int L, int max_length,
+                      int joint, float beta, int64_t pad) {
+    extern __shared__ float vsm[];
+    const int Lp = (L + 31) & ~31;
+    float *a0 = vsm, *a1 = vsm + Lp;            // alpha of two consecutive steps
+    float *lastcol = a1 + Lp;                    // links[j][ol-1]
+    float *lg = lastcol + Lp;                    // token log-probabilities of the vertices
+    __shared__ float red_v[kDecWarps];
+    __shared__ int red_i[kDecWarps];
+    __shared__ float best_score;
+    __shared__ int best_len, best_vertex;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int b = blockIdx.x;
+    const float *lk = links_all + (size_t)b * L * L;
+    const float *logit = logits_all + (size_t)b * L;
+    int32_t *trace = trace_all + (size_t)b * (max_length > 1 ? max_length - 1 : 1) * L;
+    long long oll = output_length[b];
+    if (oll < 1 || oll > L) {
+        if (tid == 0) {
+            if (status) atomicOr(status, DAT_STATUS_BAD_LENGTH);
+            out_length[b] = 0;
+            out_score[b] = -INFINITY;
+        }
+        for (int k = tid; k < max_length; k += kDecThreads) {
+            out_tokens[(size_t)b * max_length + k] = pad;
+            out_vertices[(size_t)b * max_length + k] = -1;
+        }
+        return;
+    }
+    const int last = (int)oll - 1;
+    const float l0 = joint ? logit[0] : 0.f;
+    for (int j = tid; j < L; j += kDecThreads) {
+        lg[j] = logit[j];
+        lastcol[j] = lk[(size_t)j * L + last];
+        a0[j] = (lk[j] + l0) + logit[j];     // step 0: one transition out of vertex 0 (:727-732)
+    }
+    if (tid == 0) {
+        best_score = -INFINITY;
+        best_len = 0;
+        best_vertex = 0;
+    }
+    __syncthreads();
+    for (int t = 0; t < max_length; t++) {
+        const float *cur = (t & 1) ? a1 : a0;
+        float *nxt = (t & 1) ? a0 : a1;
+        // ---- score of stopping after t+1 tokens: max_j cur[j] + links[j][last], first maximum (:747-752)
+        float sv = -INFINITY;
+        int si = INT_MAX;
+        for (int j = tid; j < L; j += kDecThreads) {
+            const float v = cur[j] + lastcol[j];
+            if (v != v) { sv = v; si = j < si ? j : si; }   // NaN counts as the maximum, like torch.max
+            else if (!(sv != sv)) vit_better(sv, si, v, j);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, sv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, si, o);
+            if (ov != ov) { if (!(sv != sv) || oi < si) { sv = ov; si = oi; } }
+            else if (!(sv != sv)) vit_better(sv, si, ov, oi);
+        }
+        if (lane == 0) { red_v[warp] = sv; red_i[warp] = si; }
+        __syncthreads();
+        if (tid == 0) {
+            float v = red_v[0];
+            int i = red_i[0];
+            for (int w = 1; w < kDecWarps; w++) {
+                const float ov = red_v[w];
+                const int oi = red_i[w];
+                if (ov != ov) { if (!(v != v) || oi < i) { v = ov; i = oi; } }
+                else if (!(v != v)) vit_better(v, i, ov, oi);
+            }
+            if (i == INT_MAX) i = 0;
+            const float sc = v / powf((float)(t + 1), beta);
+            // first maximum over the lengths (:754)
+            if (t == 0 || sc > best_score || (sc != sc && !(best_score != best_score))) {
+                best_score = sc;
+                best_len = t + 1;
+                best_vertex = i;
+            }
+        }
+        if (t + 1 == max_length) break;
+        // ---- next step: nxt[j] = max_i cur[i] + links[i][j], first maximum (:737-742)
+        for (int j = tid; j < L; j += kDecThreads) {
+            float bv = -INFINITY;
+            int bi = INT_MAX;
+            bool nan = false;
+            const float *col = lk + j;
+#pragma unroll 4
+            for (int i = 0; i < L; i++) {
+                const float v = cur[i] + __ldg(col + (size_t)i * L);
+                if (v != v) { if (!nan) { nan = true; bv = v; bi = i; } }
+                else if (!nan && v > bv) { bv = v; bi = i; }
+            }
+            if (bi == INT_MAX) bi = 0;          // every candidate is -inf: torch returns index 0
+            trace[(size_t)t * L + j] = bi;
+            nxt[j] = joint ? bv + lg[j] : bv;
+        }
+        __syncthreads();
+    }
+    __syncthreads();
+    // ---- back-trace and token collapse by one thread (<= max_length steps; :757-771)
+    if (tid == 0) {
+        const int len = best_len;
+        int64_t *vert = out_vertices + (size_t)b * max_length;
+        int64_t *tok = out_tokens + (size_t)b * max_length;
+        const int64_t *tokens = tokens_all + (size_t)b * L;
+        int j = best_vertex;
+        for (int k = len - 1; k >= 0; k--) {
+            vert[k] = j;
+            if (k > 0) j = trace[(size_t)(k - 1) * L + j];
+        }
+        for (int k = len; k < max_length; k++) vert[k] = -1;
+        // walk from the end: a token is kept unless it is pad or equals the token that follows it;
+        // the final token is always kept.  Kept tokens are written right-aligned, then shifted left.
+        int64_t lastt = tokens[vert[len - 1]];
+        int w = max_length - 1;
+        tok[w--] = lastt;
+        for (int k = len - 2; k >= 0; k--) {
+            const int64_t now = tokens[vert[k]];
+            if (now != pad && now != lastt) tok[w--] = now;
+            lastt = now;
+        }
+        const int n = max_length - 1 - w;
+        for (int k = 0; k < n; k++) tok[k] = tok[w + 1 + k];
+        for (int k = n; k < max_length; k++) tok[k] = pad;
+        out_length[b] = n;
+        out_score[b] = best_score;
+    }
+}
+
+}  // namespace dat
+
+extern "C" {
+
+int dat_node_passing_prob(const float *links_square, float *node_pass, int bsz, int prelen, void *stream) {
+    using namespace dat;
+    DAT_REQUIRE(bsz >= 0 && prelen >= 1, DAT_ERR_BAD_ARG, "dat_node_passing_prob: bad sizes bsz=%d prelen=%d",
+                bsz, prelen);
+    if (bsz == 0) return DAT_OK;
+    DAT_REQUIRE(links_square && node_pass, DAT_ERR_BAD_ARG, "dat_node_passing_prob: null pointer");
+    DAT_REQUIRE(prelen <= 8192, DAT_ERR_UNSUPPORTED, "dat_node_passing_prob: prelen=%d exceeds 8192", prelen);
+    const size_t smem = ((size_t)((prelen + 31) & ~31) + 8 * 32) * sizeof(float);
+    node_pass_kernel<<<(unsigned)bsz, 256, smem, static_cast<cudaStream_t>(stream)>>>(links_square, node_pass,
+                                                                                    prelen);
+    return check_launch("dat_node_passing_prob");
+}
+
+size_t dat_viterbi_decode_workspace_bytes(int bsz, int prelen, int max_length) {
+    if (bsz <= 0 || prelen <= 0 || max_length <= 0) return 0;
+    return (size_t)bsz * (size_t)(max_length > 1 ? max_length - 1 : 1) * prelen * sizeof(int32_t);
+}
+
+int dat_viterbi_decode(const float *links_square, const float *unreduced_logits,
+                       const int64_t *unreduced_tokens, const int64_t *output_length, void *workspace,
+                       int64_t *out_tokens, int64_t *out_length, int64_t *out_vertices, float *out_score,
+                       int32_t *status, int bsz, int prelen, int max_length, int joint, float beta,
+                       int64_t pad_index, void *stream) {
+    using namespace dat;
+    const char *who = "dat_viterbi_decode";
+    DAT_REQUIRE(bsz >= 0 && prelen >= 1 && max_length >= 1, DAT_ERR_BAD_ARG,
+                "%s: bad sizes bsz=%d prelen=%d max_length=%d", who, bsz, prelen, max_length);
+    if (bsz == 0) return DAT_OK;
+    DAT_REQUIRE(links_square && unreduced_logits && unreduced_tokens && output_length && workspace &&
+                    out_tokens && out_length && out_vertices && out_score,
+                DAT_ERR_BAD_ARG, "%s: null pointer", who);
+    DAT_REQUIRE(prelen <= 8192, DAT_ERR_UNSUPPORTED, "%s: prelen=%d exceeds 8192", who, prelen);
+    const size_t smem = (size_t)4 * ((prelen + 31) & ~31) * sizeof(float);
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(viterbi_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+            cudaSuccess)
+        return check_launch(who);
+    viterbi_decode_kernel<<<(unsigned)bsz, kDecThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        links_square, unreduced_logits, unreduced_tokens, output_length, static_cast<int32_t *>(workspace),
+        out_tokens, out_length, out_vertices, out_score, status, prelen, max_length, joint, beta, pad_index);
+    return check_launch(who);
+}
+
+}  // extern "C"

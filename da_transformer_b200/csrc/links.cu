@@ -1,0 +1,275 @@
+// Transition scores -> band links, forward and backward, for sm_100a.
+//
+// Replaces the tail of GlatDecomposedLink.extract_links
+// (fs_plugins/models/glat_decomposed_with_link.py:380-404, with extract_valid_links :319-335):
+// from the per-head scores  content[b,i,j,h]  (log_multi_content, [B,L,L,H] fp32) and the
+// per-vertex head log-probabilities  log_gates[b,i,h]  it produces the band
+//     links[b,i,d] = logsumexp_h( log_softmax_j(content[b,i,.,h])[j] + log_gates[b,i,h] ),  j = i+d+1,
+// where the softmax runs over the valid successors of i inside the band (j in (i, i+K], j < L,
+// column allowed by the mask); invalid entries and vertices without any successor are -inf.
+// The reference materialises [B,L,K,H] three times on the way (gather, log_softmax, + gates).
+// Here one CTA owns one vertex (b,i): it stages the H x (valid successors) scores once in shared
+// memory, reduces per head, and writes the K band entries; nothing else touches HBM.
+//
+// HBM-bound.  Algorithmic bytes: forward reads the upper triangle of content once
+// (~ B*L*L*H*4 / 2) and writes B*L*K*4; backward reads the same triangle plus the band gradient and
+// writes the dense [B,L,L,H] gradient once (zeros included, like autograd's result).
+#include "dat_common.cuh"
+
+namespace dat {
+
+constexpr int kLinksThreads = 256;
+
+struct LinksMask {
+    const int64_t *bound_end;      // [B, L]: successors j <= bound_end[b,i] (decoding), or null
+    const unsigned char *nonpad;   // [B, L]: successor j allowed iff nonpad[b,j] != 0 (training), or null
+};
+
+// first / last successor of vertex i inside the band and the graph: j in [i+1, jhi]
+__device__ __forceinline__ int links_jhi(int i, int L, int K, const LinksMask &mk, int64_t row) {
+    int jhi = i + K < L - 1 ? i + K : L - 1;
+    if (mk.bound_end) {
+        const int64_t be = mk.bound_end[row];
+        jhi = be < jhi ? (int)be : jhi;
+    }
+    return jhi;
+}
+
+// Stages content[b,i,j,:] for j in [i+1, jhi] into sm[(j-i-1)*H + h]; masked columns become -inf.
+__device__ __forceinline__ void links_stage_row(const float *__restrict__ crow, float *sm, int i, int jhi,
+                                                int H, const unsigned char *np_row) {
+    const int n = (jhi - i) * H;   // may be <= 0
+    const float *src = crow + (size_t)(i + 1) * H;
+    if ((H & 3) == 0) {
+        const float4 *s4 = reinterpret_cast<const float4 *>(src);
+        float4 *d4 = reinterpret_cast<float4 *>(sm);
+        for (int x = threadIdx.x; x < n / 4; x += kLinksThreads) {
+            float4 v = __ldg(s4 + x);
+            if (np_row && !np_row[i + 1 + (4 * x) / H]) v = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            d4[x] = v;
+        }
+    } else {
+        for (int x = threadIdx.x; x < n; x += kLinksThreads) {
+            float v = __ldg(src + x);
+            if (np_row && !np_row[i + 1 + x / H]) v = -INFINITY;
+            sm[x] = v;
+        }
+    }
+}
+
+// Per-head log-sum-exp (natural log) over the staged successors.  Thread (h = tid % H, part = tid / H)
+// walks the successors part, part + P, ...; partial (max, sum) pairs meet in shared memory.
+// Result in lse_s[h] (-inf when the head sees no finite score).  Needs H <= kLinksThreads.
+__device__ __forceinline__ void links_head_lse(const float *sm, int nj, int H, float *part_m, float *part_s,
+                                               float *lse_s) {
+    const int tid = threadIdx.x;
+    const int P = kLinksThreads / H;
+    const int h = tid % H, part = tid / H;
+    float m = kNegBig, s = 0.f;
+    if (part < P) {
+        for (int j = part; j < nj; j += P) {
+            const float v = sm[j * H + h] * kLog2e;
+            if (v > m) {
+                s *= ex2(m - v);
+                m = v;
+            }
+            s += ex2(v - m);
+        }
+        part_m[part * H + h] = m;
+        part_s[part * H + h] = s;
+    }
+    __syncthreads();
+    if (tid < H) {
+        float M = kNegBig, S = 0.f;
+        for (int p = 0; p < P; p++) lse_merge(M, S, part_m[p * H + tid], part_s[p * H + tid]);
+        lse_s[tid] = (S > 0.f && M > 0.5f * kNegBig) ? (M + lg2(S)) * kLn2 : -INFINITY;
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(kLinksThreads)
+links_fwd_kernel(const float *__restrict__ content, const float *__restrict__ log_gates, LinksMask mk,
+                 float *__restrict__ links, float *__restrict__ head_lse, int L, int H, int K) {
+    extern __shared__ __align__(16) float lsm[];
+    const int64_t row = blockIdx.x;          // b * L + i
+    const int i = (int)(row % L);
+    const int64_t b = row / L;
+    const int tid = threadIdx.x;
+    float *sm = lsm;                          // [(L-1) * H] staged scores
+    float *part_m = sm + (size_t)(L - 1) * H; // [P * H]
+    float *part_s = part_m + kLinksThreads;
+    float *lse_s = part_s + kLinksThreads;    // [H]
+    float *gate_s = lse_s + H;                // [H]
+    const int jhi = links_jhi(i, L, K, mk, row);
+    const int nj = jhi - i > 0 ? jhi - i : 0;
+    const unsigned char *np_row = mk.nonpad ? mk.nonpad + b * L : nullptr;
+    links_stage_row(content + row * (size_t)L * H, sm, i, jhi, H, np_row);
+    if (tid < H) gate_s[tid] = log_gates[row * H + tid];
+    __syncthreads();
+    links_head_lse(sm, nj, H, part_m, part_s, lse_s);
+    if (head_lse && tid < H) head_lse[row * H + tid] = lse_s[tid];
+    float *out = links + row * (size_t)K;
+    for (int d = tid; d < K; d += kLinksThreads) {
+        float v = -INFINITY;
+        if (d < nj) {
+            float m = kNegBig, s = 0.f;
+            for (int h = 0; h < H; h++) {
+                // a head whose every score is -inf has lse = -inf: z is NaN there and is skipped
+                const float z = ((sm[d * H + h] - lse_s[h]) + gate_s[h]) * kLog2e;
+                if (z > m) {
+                    s *= ex2(m - z);
+                    m = z;
+                }
+                if (z == z) s += ex2(z - m);
+            }
+            if (s > 0.f && m > 0.5f * kNegBig) v = (m + lg2(s)) * kLn2;
+        }
+        out[d] = v;
+    }
+}
+
+// Backward.  With z[j,h] = c[j,h] - lse_h + g_h, links[j] = logsumexp_h z[j,h], G[j] the incoming
+// gradient and p[j,h] = exp(z[j,h] - links[j]):
+//     S_h          = sum_j G[j] p[j,h]                          = d / d log_gates[h]
+//     d / d c[j,h] = G[j] p[j,h] - exp(c[j,h] - lse_h) * S_h
+// grad_content is written for the whole [L,H] row (zeros outside the valid successors); it may alias
+// content (a CTA has its row in shared memory before it writes).
+__global__ void __launch_bounds__(kLinksThreads)
+links_bwd_kernel(const float *__restrict__ grad_links, const float *content,
+                 const float *__restrict__ log_gates, const float *__restrict__ links,
+                 const float *__restrict__ head_lse, LinksMask mk, float *grad_content,
+                 float *__restrict__ grad_log_gates, int L, int H, int K) {
+    extern __shared__ __align__(16) float lsm[];
+    const int64_t row = blockIdx.x;
+    const int i = (int)(row % L);
+    const int64_t b = row / L;
+    const int tid = threadIdx.x;
+    float *sm = lsm;                           // [(L-1) * H]
+    float *gl_s = sm + (size_t)(L - 1) * H;    // [L-1] incoming gradient per successor
+    float *lk_s = gl_s + (L - 1);              // [L-1] forward value per successor
+    float *part = lk_s + (L - 1);              // [kLinksThreads]
+    float *lse_s = part + kLinksThreads;       // [H]
+    float *gate_s = lse_s + H;                 // [H]
+    float *S_s = gate_s + H;                   // [H]
+    const int jhi = links_jhi(i, L, K, mk, row);
+    const int nj = jhi - i > 0 ? jhi - i : 0;
+    const unsigned char *np_row = mk.nonpad ? mk.nonpad + b * L : nullptr;
+    links_stage_row(content + row * (size_t)L * H, sm, i, jhi, H, np_row);
+    for (int d = tid; d < nj; d += kLinksThreads) {
+        gl_s[d] = grad_links[row * (size_t)K + d];
+        lk_s[d] = links[row * (size_t)K + d];
+    }
+    if (tid < H) {
+        gate_s[tid] = log_gates[row * H + tid];
+        lse_s[tid] = head_lse[row * H + tid];
+    }
+    __syncthreads();
+    // S_h: thread (h, part) sums over its successors
+    const int P = kLinksThreads / H;
+    const int h = tid % H, pt = tid / H;
+    float acc = 0.f;
+    if (pt < P) {
+        const float k = (gate_s[h] - lse_s[h]) * kLog2e;
+        if (lse_s[h] > -INFINITY)
+            for (int j = pt; j < nj; j += P) {
+                const float lk = lk_s[j];
+                if (lk > -INFINITY) acc += gl_s[j] * ex2(fmaf(sm[j * H + h], kLog2e, k) - lk * kLog2e);
+            }
+        part[pt * H + h] = acc;
+    }
+    __syncthreads();
+    if (tid < H) {
+        float S = 0.f;
+        for (int p = 0; p < P; p++) S += part[p * H + tid];
+        S_s[tid] = S;
+        grad_log_gates[row * H + tid] = S;
+    }
+    __syncthreads();
+    // the dense gradient row: zeros for j <= i and past the valid successors
+    float *grow = grad_content + row * (size_t)L * H;
+    const int total = L * H;
+    for (int x = tid; x < total; x += kLinksThreads) {
+        const int j = x / H, hh = x - j * H;
+        float v = 0.f;
+        const int d = j - i - 1;
+        if (d >= 0 && d < nj) {
+            const float c = sm[d * H + hh], lse = lse_s[hh], lk = lk_s[d];
+            if (c > -INFINITY && lse > -INFINITY) {
+                const float soft = ex2((c - lse) * kLog2e);
+                float pg = 0.f;
+                if (lk > -INFINITY) pg = gl_s[d] * ex2(((c - lse) + gate_s[hh] - lk) * kLog2e);
+                v = pg - soft * S_s[hh];
+            }
+        }
+        grow[x] = v;
+    }
+}
+
+static size_t links_smem_fwd(int L, int H) {
+    return ((size_t)(L - 1) * H + 2 * kLinksThreads + 2 * H) * sizeof(float) + 16;
+}
+static size_t links_smem_bwd(int L, int H) {
+    return ((size_t)(L - 1) * H + 2 * (size_t)(L - 1) + kLinksThreads + 3 * H) * sizeof(float) + 16;
+}
+
+}  // namespace dat
+
+extern "C" {
+
+int dat_links_from_heads(const float *content, const float *log_gates, const int64_t *bound_end,
+                         const unsigned char *nonpad, float *links, float *head_lse, int bsz,
+                         int prelen, int heads, int translen, void *stream) {
+    using namespace dat;
+    const char *who = "dat_links_from_heads";
+    DAT_REQUIRE(bsz >= 0 && prelen >= 1 && heads >= 1 && translen >= 1, DAT_ERR_BAD_ARG,
+                "%s: bad sizes bsz=%d prelen=%d heads=%d translen=%d", who, bsz, prelen, heads, translen);
+    if (bsz == 0) return DAT_OK;
+    DAT_REQUIRE(content && log_gates && links, DAT_ERR_BAD_ARG, "%s: null pointer", who);
+    DAT_REQUIRE(heads <= kLinksThreads, DAT_ERR_UNSUPPORTED, "%s: heads=%d exceeds %d", who, heads,
+                kLinksThreads);
+    DeviceInfo di;
+    if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
+    const size_t smem = links_smem_fwd(prelen, heads);
+    DAT_REQUIRE(smem <= (size_t)di.max_smem_optin, DAT_ERR_UNSUPPORTED,
+                "%s: prelen*heads = %d*%d needs %zu bytes of shared memory", who, prelen, heads, smem);
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(links_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+            cudaSuccess)
+        return check_launch(who);
+    const LinksMask mk{bound_end, nonpad};
+    links_fwd_kernel<<<(unsigned)((size_t)bsz * prelen), kLinksThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        content, log_gates, mk, links, head_lse, prelen, heads, translen);
+    return check_launch(who);
+}
+
+int dat_links_from_heads_backward(const float *grad_links, const float *content, const float *log_gates,
+                                  const float *links, const float *head_lse, const int64_t *bound_end,
+                                  const unsigned char *nonpad, float *grad_content,
+                                  float *grad_log_gates, int bsz, int prelen, int heads, int translen,
+                                  void *stream) {
+    using namespace dat;
+    const char *who = "dat_links_from_heads_backward";
+    DAT_REQUIRE(bsz >= 0 && prelen >= 1 && heads >= 1 && translen >= 1, DAT_ERR_BAD_ARG,
+                "%s: bad sizes bsz=%d prelen=%d heads=%d translen=%d", who, bsz, prelen, heads, translen);
+    if (bsz == 0) return DAT_OK;
+    DAT_REQUIRE(grad_links && content && log_gates && links && head_lse && grad_content && grad_log_gates,
+                DAT_ERR_BAD_ARG, "%s: null pointer", who);
+    DAT_REQUIRE(heads <= kLinksThreads, DAT_ERR_UNSUPPORTED, "%s: heads=%d exceeds %d", who, heads,
+                kLinksThreads);
+    DeviceInfo di;
+    if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
+    const size_t smem = links_smem_bwd(prelen, heads);
+    DAT_REQUIRE(smem <= (size_t)di.max_smem_optin, DAT_ERR_UNSUPPORTED,
+                "%s: prelen*heads = %d*%d needs %zu bytes of shared memory", who, prelen, heads, smem);
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(links_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+            cudaSuccess)
+        return check_launch(who);
+    const LinksMask mk{bound_end, nonpad};
+    links_bwd_kernel<<<(unsigned)((size_t)bsz * prelen), kLinksThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        grad_links, content, log_gates, links, head_lse, mk, grad_content, grad_log_gates, prelen, heads,
+        translen);
+    return check_launch(who);
+}
+
+}  // extern "C"

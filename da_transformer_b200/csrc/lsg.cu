@@ -10,17 +10,25 @@
 //
 // HBM-bound: algorithmic bytes are V*e per row forward and 2*V*e per row backward
 // (e = element size), plus the small index / gathered-value traffic.
+//
+// Two things the criterion does around the gather ride on the same pass when asked for
+// (dat_logsoftmax_gather_fused):
+//   * the arg-max token of every row, which the glancing sampler takes with a separate full read of
+//     the logits right before its gather (fs_plugins/criterions/nat_dag_loss.py:246), with
+//     torch.argmax's result for ties (first index) and NaN (counts as the maximum);
+//   * the forced alignment (nat_dag_loss.py:111-120): a target step that some vertex is forced to
+//     emit keeps only that vertex (0 there, -inf at every other vertex), and no gradient flows
+//     into the forced steps.  The reference builds three [B,T,L] temporaries for it.
+#include <climits>
+
 #include "dat_common.cuh"
 
 namespace dat {
 
 constexpr int kLsgThreads = 256;
 constexpr int kLsgWarps = kLsgThreads / 32;
-#ifndef DAT_BWD_UNROLL
-#define DAT_BWD_UNROLL 4
-#endif
-constexpr int kBwdUnroll = DAT_BWD_UNROLL;
-constexpr int kFwdStage = 512;           // selected logits staged per row in the forward  // 16-byte vectors in flight per thread in the backward
+constexpr int kBwdUnroll = 4;   // 16-byte vectors in flight per thread in the backward
+constexpr int kFwdStage = 512;  // selected logits staged per row in the forward
 
 struct Strides3 {
     int64_t b, l, s;
@@ -63,17 +71,36 @@ __device__ __forceinline__ void row_split(const T *p, int V, int &head, int &nve
     nvec = (V - head) / kVec;
 }
 
-template <typename T>
+// Optional extras of the forward pass (all null for the plain gather).
+struct LsgExtras {
+    int64_t *argmax;             // [rows]: arg-max token of each row
+    const int64_t *force_emit;   // [B, L] contiguous: target step vertex l is forced to emit, or -1
+    const int32_t *forced_step;  // [B, S]: 1 where some vertex of the sentence is forced to emit step s
+};
+
+// (value, index) pair ordered like torch.argmax orders candidates: larger value first, then smaller index
+__device__ __forceinline__ void arg_better(float &bm, int &bi, float v, int i) {
+    if (v > bm || (v == bm && i < bi)) {
+        bm = v;
+        bi = i;
+    }
+}
+
+template <typename T, bool kArgmax>
 __global__ void __launch_bounds__(kLsgThreads)
 lsg_fwd_kernel(const T *__restrict__ x, const int64_t *__restrict__ idx, Strides3 is,
                float *__restrict__ sel, Strides3 ss, float *__restrict__ stats,
-               int32_t *__restrict__ status, int64_t rows, int L, int S, int V) {
+               int32_t *__restrict__ status, LsgExtras ex, int64_t rows, int L, int S, int V) {
     constexpr int kVec = Elem<T>::kVec;
     __shared__ float red_m[2][kLsgWarps];
     __shared__ float red_s[2][kLsgWarps];
+    __shared__ float arg_m[2][kLsgWarps];
+    __shared__ int arg_i[2][kLsgWarps];
+    __shared__ int arg_nan[2][kLsgWarps];
     __shared__ float xsel[2][kFwdStage];   // logits at the first kFwdStage selected positions
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int par = 0;
+    bool bad_index = false;
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, par ^= 1) {
         const T *xr = x + row * (int64_t)V;
         const int64_t b = row / L, l = row - b * L;
@@ -83,12 +110,16 @@ lsg_fwd_kernel(const T *__restrict__ x, const int64_t *__restrict__ idx, Strides
         // streaming loads do not keep the row in cache) and cost an extra ~12 % of traffic.
         for (int k = tid; k < S && k < kFwdStage; k += kLsgThreads) {
             const int64_t id = ir[(int64_t)k * is.s];
-            xsel[par][k] = (id >= 0 && id < V) ? Elem<T>::to_float(xr[id]) : __int_as_float(0x7fc00000);
+            const bool ok = id >= 0 && id < V;
+            bad_index |= !ok;
+            xsel[par][k] = ok ? Elem<T>::to_float(xr[id]) : __int_as_float(0x7fc00000);
         }
         int head, nvec;
         row_split(xr, V, head, nvec);
         const uint4 *xv = reinterpret_cast<const uint4 *>(xr + head);
         float m = kNegBig, s = 0.f;
+        float bm = -INFINITY;   // arg-max candidate of this thread (kArgmax only)
+        int bi = INT_MAX;
         int v = tid;
         for (; v + 3 * kLsgThreads < nvec; v += 4 * kLsgThreads) {
             uint4 u0 = ld_stream16(xv + v);
@@ -100,22 +131,58 @@ lsg_fwd_kernel(const T *__restrict__ x, const int64_t *__restrict__ idx, Strides
             Elem<T>::unpack(u1, f + kVec);
             Elem<T>::unpack(u2, f + 2 * kVec);
             Elem<T>::unpack(u3, f + 3 * kVec);
+            if (kArgmax) {
+                // a thread meets its elements in increasing index order, so a strictly larger
+                // group maximum is the only way its candidate changes (rare after the first groups)
+                float gm = f[0];
+#pragma unroll
+                for (int i = 1; i < 4 * kVec; i++) gm = fmaxf(gm, f[i]);
+                if (gm > bm) {
+                    bm = gm;
+#pragma unroll
+                    for (int i = 4 * kVec - 1; i >= 0; i--)
+                        if (f[i] == gm) bi = head + (v + (i / kVec) * kLsgThreads) * kVec + (i % kVec);
+                }
+            }
             online_update<4 * kVec>(m, s, f);
         }
         for (; v < nvec; v += kLsgThreads) {
             uint4 u0 = ld_stream16(xv + v);
             float f[kVec];
             Elem<T>::unpack(u0, f);
+            if (kArgmax) {
+#pragma unroll
+                for (int i = 0; i < kVec; i++) arg_better(bm, bi, f[i], head + v * kVec + i);
+            }
             online_update<kVec>(m, s, f);
         }
         // scalar head and tail
         const int tail0 = head + nvec * kVec;
-        if (tid < head) online_update1(m, s, Elem<T>::to_float(xr[tid]));
-        if (tail0 + tid < V) online_update1(m, s, Elem<T>::to_float(xr[tail0 + tid]));
+        if (tid < head) {
+            const float xv0 = Elem<T>::to_float(xr[tid]);
+            if (kArgmax) arg_better(bm, bi, xv0, tid);
+            online_update1(m, s, xv0);
+        }
+        if (tail0 + tid < V) {
+            const float xv0 = Elem<T>::to_float(xr[tail0 + tid]);
+            if (kArgmax) arg_better(bm, bi, xv0, tail0 + tid);
+            online_update1(m, s, xv0);
+        }
 
         // block max (exact), then block sum of the rescaled partial sums
         float wm = warp_max(m);
-        if (lane == 0) red_m[par][warp] = wm;
+        if (kArgmax) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bm, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                arg_better(bm, bi, ov, oi);
+            }
+        }
+        if (lane == 0) {
+            red_m[par][warp] = wm;
+            if (kArgmax) { arg_m[par][warp] = bm; arg_i[par][warp] = bi; }
+        }
         __syncthreads();
         float M = red_m[par][0];
 #pragma unroll
@@ -129,23 +196,90 @@ lsg_fwd_kernel(const T *__restrict__ x, const int64_t *__restrict__ idx, Strides
         for (int w = 0; w < kLsgWarps; w++) Ssum += red_s[par][w];
         const float logS = lg2(Ssum) * kLn2;
 
+        if (kArgmax) {
+            float am = arg_m[par][0];
+            int ai = arg_i[par][0];
+#pragma unroll
+            for (int w = 1; w < kLsgWarps; w++) arg_better(am, ai, arg_m[par][w], arg_i[par][w]);
+            // A NaN or +inf logit, or a row of -inf, shows as a sum that is not a positive finite
+            // number (fmaxf skips NaN, so the candidates above never saw it).  Such rows are scanned
+            // again with torch.argmax's rules: the first NaN if there is one, else the first maximum.
+            if (!(Ssum > 0.f && Ssum < INFINITY) || ai == INT_MAX) {   // block-uniform
+                float sm2 = -INFINITY;
+                int si = INT_MAX, sn = INT_MAX;
+                for (int e = tid; e < V; e += kLsgThreads) {
+                    const float xe = Elem<T>::to_float(xr[e]);
+                    if (xe != xe) sn = e < sn ? e : sn;
+                    else arg_better(sm2, si, xe, e);
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, sm2, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, si, o);
+                    const int on = __shfl_xor_sync(0xffffffffu, sn, o);
+                    arg_better(sm2, si, ov, oi);
+                    sn = on < sn ? on : sn;
+                }
+                __syncthreads();   // everybody has read the first reduction's slots
+                if (lane == 0) { arg_m[par][warp] = sm2; arg_i[par][warp] = si; arg_nan[par][warp] = sn; }
+                __syncthreads();
+                am = arg_m[par][0];
+                ai = arg_i[par][0];
+                int an = arg_nan[par][0];
+#pragma unroll
+                for (int w = 1; w < kLsgWarps; w++) {
+                    arg_better(am, ai, arg_m[par][w], arg_i[par][w]);
+                    an = arg_nan[par][w] < an ? arg_nan[par][w] : an;
+                }
+                if (an != INT_MAX) ai = an;
+                else if (ai == INT_MAX) ai = 0;
+            }
+            if (tid == 0) ex.argmax[row] = ai;
+        }
+
         float *sr = sel + b * ss.b + l * ss.l;
+        const int64_t fe = ex.force_emit ? ex.force_emit[row] : -1;
+        const int32_t *forced = ex.forced_step ? ex.forced_step + b * S : nullptr;
         for (int k = tid; k < S; k += kLsgThreads) {
             float xv_k;
             if (k < kFwdStage) {
                 xv_k = xsel[par][k];   // written by this same thread above
             } else {
                 const int64_t id = ir[(int64_t)k * is.s];
-                xv_k = (id >= 0 && id < V) ? Elem<T>::to_float(xr[id]) : __int_as_float(0x7fc00000);
+                const bool ok = id >= 0 && id < V;
+                bad_index |= !ok;
+                xv_k = ok ? Elem<T>::to_float(xr[id]) : __int_as_float(0x7fc00000);
             }
-            if (!(xv_k == xv_k) && status) atomicOr(status, DAT_STATUS_BAD_INDEX);
-            sr[(int64_t)k * ss.s] = (xv_k - M) - logS;
+            float out = (xv_k - M) - logS;
+            if (forced && forced[k]) out = (fe == k) ? 0.f : -INFINITY;
+            sr[(int64_t)k * ss.s] = out;
         }
         if (stats != nullptr && tid == 0) {
             stats[2 * row] = M;
             stats[2 * row + 1] = logS;
         }
     }
+    if (bad_index && status) atomicOr(status, DAT_STATUS_BAD_INDEX);
+}
+
+// forced_step[b, s] = 1 if some vertex of sentence b is forced to emit target step s
+// (the reference's matchmask.sum(-1) > 0, nat_dag_loss.py:114-116).  One CTA per sentence.
+__global__ void __launch_bounds__(256)
+lsg_forced_steps_kernel(const int64_t *__restrict__ force_emit, int32_t *__restrict__ forced_step,
+                        int32_t *__restrict__ status, int L, int S) {
+    extern __shared__ int32_t fs_s[];
+    const int b = blockIdx.x;
+    for (int k = threadIdx.x; k < S; k += blockDim.x) fs_s[k] = 0;
+    __syncthreads();
+    bool bad = false;
+    for (int l = threadIdx.x; l < L; l += blockDim.x) {
+        const int64_t t = force_emit[(int64_t)b * L + l];
+        if (t >= 0 && t < S) fs_s[t] = 1;   // benign race: every writer stores 1
+        else bad |= t >= S;
+    }
+    __syncthreads();
+    for (int k = threadIdx.x; k < S; k += blockDim.x) forced_step[(int64_t)b * S + k] = fs_s[k];
+    if (bad && status) atomicOr(status, DAT_STATUS_BAD_INDEX);
 }
 
 // Backward, in place.  Shared memory: S * (int + 3 float).
@@ -153,7 +287,7 @@ template <typename T>
 __global__ void __launch_bounds__(kLsgThreads)
 lsg_bwd_kernel(T *__restrict__ x, const int64_t *__restrict__ idx, Strides3 is,
                const float *__restrict__ g, Strides3 gs, const float *__restrict__ stats,
-               int64_t rows, int L, int S, int V) {
+               const int32_t *__restrict__ forced_step, int64_t rows, int L, int S, int V) {
     constexpr int kVec = Elem<T>::kVec;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     int *idx_s = reinterpret_cast<int *>(smem_raw);
@@ -171,9 +305,11 @@ lsg_bwd_kernel(T *__restrict__ x, const int64_t *__restrict__ idx, Strides3 is,
         __syncthreads();  // previous row's fix-ups are done with the staging arrays
         float gsum = 0.f;
         int nonzero = 0;
+        const int32_t *forced = forced_step ? forced_step + b * S : nullptr;
         for (int k = tid; k < S; k += kLsgThreads) {
             int64_t id = ir[(int64_t)k * is.s];
             float gv = gr[(int64_t)k * gs.s];
+            if (forced && forced[k]) gv = 0.f;   // a forced step's match value is a constant
             bool ok = id >= 0 && id < V;
             idx_s[k] = ok ? (int)id : -1;
             g_s[k] = ok ? gv : 0.f;
@@ -248,31 +384,39 @@ lsg_bwd_kernel(T *__restrict__ x, const int64_t *__restrict__ idx, Strides3 is,
     }
 }
 
-template <typename T>
-static int launch_fwd(const void *x, const int64_t *idx, Strides3 is, float *sel, Strides3 ss,
-                      float *stats, int32_t *status, int64_t rows, int L, int S, int V,
-                      cudaStream_t stream, const DeviceInfo &di) {
+template <typename T, bool kArgmax>
+static int launch_fwd_t(const void *x, const int64_t *idx, Strides3 is, float *sel, Strides3 ss,
+                        float *stats, int32_t *status, const LsgExtras &ex, int64_t rows, int L, int S,
+                        int V, cudaStream_t stream, const DeviceInfo &di, const char *who) {
     int per_sm = 0;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lsg_fwd_kernel<T>, kLsgThreads, 0);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lsg_fwd_kernel<T, kArgmax>, kLsgThreads, 0);
     if (per_sm < 1) per_sm = 1;
     int64_t grid = (int64_t)di.sm_count * per_sm;
     if (grid > rows) grid = rows;
-    lsg_fwd_kernel<T><<<(unsigned)grid, kLsgThreads, 0, stream>>>(
-        static_cast<const T *>(x), idx, is, sel, ss, stats, status, rows, L, S, V);
-    return check_launch("dat_logsoftmax_gather");
+    lsg_fwd_kernel<T, kArgmax><<<(unsigned)grid, kLsgThreads, 0, stream>>>(
+        static_cast<const T *>(x), idx, is, sel, ss, stats, status, ex, rows, L, S, V);
+    return check_launch(who);
+}
+
+template <typename T>
+static int launch_fwd(const void *x, const int64_t *idx, Strides3 is, float *sel, Strides3 ss,
+                      float *stats, int32_t *status, const LsgExtras &ex, int64_t rows, int L, int S,
+                      int V, cudaStream_t stream, const DeviceInfo &di, const char *who) {
+    return ex.argmax ? launch_fwd_t<T, true>(x, idx, is, sel, ss, stats, status, ex, rows, L, S, V, stream, di, who)
+                     : launch_fwd_t<T, false>(x, idx, is, sel, ss, stats, status, ex, rows, L, S, V, stream, di, who);
 }
 
 template <typename T>
 static int launch_bwd(void *x, const int64_t *idx, Strides3 is, const float *g, Strides3 gs,
-                      const float *stats, int64_t rows, int L, int S, int V, cudaStream_t stream,
-                      const DeviceInfo &di) {
+                      const float *stats, const int32_t *forced_step, int64_t rows, int L, int S, int V,
+                      cudaStream_t stream, const DeviceInfo &di, const char *who) {
     size_t smem = (size_t)S * 16;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(lsg_bwd_kernel<T>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
             cudaGetLastError();
-            set_error("dat_logsoftmax_gather_backward: cannot reserve %zu bytes of shared memory", smem);
+            set_error("%s: cannot reserve %zu bytes of shared memory", who, smem);
             return DAT_ERR_UNSUPPORTED;
         }
     }
@@ -282,8 +426,65 @@ static int launch_bwd(void *x, const int64_t *idx, Strides3 is, const float *g, 
     int64_t grid = (int64_t)di.sm_count * per_sm;
     if (grid > rows) grid = rows;
     lsg_bwd_kernel<T><<<(unsigned)grid, kLsgThreads, smem, stream>>>(
-        static_cast<T *>(x), idx, is, g, gs, stats, rows, L, S, V);
-    return check_launch("dat_logsoftmax_gather_backward");
+        static_cast<T *>(x), idx, is, g, gs, stats, forced_step, rows, L, S, V);
+    return check_launch(who);
+}
+
+static int gather_forward(const void *word_ins_out, int dtype, const int64_t *select_idx, Strides3 is,
+                          float *selected_result, Strides3 ss, float *row_stats, int32_t *status,
+                          const LsgExtras &ex, int bsz, int prelen, int slen, int vocab,
+                          cudaStream_t st, const char *who) {
+    DAT_REQUIRE(bsz >= 0 && prelen >= 0 && slen >= 0 && vocab >= 1, DAT_ERR_BAD_ARG,
+                "%s: bad sizes bsz=%d prelen=%d slen=%d vocab=%d", who, bsz, prelen, slen, vocab);
+    if ((int64_t)bsz * prelen == 0) return DAT_OK;
+    DAT_REQUIRE(word_ins_out && (slen == 0 || (select_idx && selected_result)), DAT_ERR_BAD_ARG,
+                "%s: null pointer", who);
+    DeviceInfo di;
+    if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
+    const int64_t rows = (int64_t)bsz * prelen;
+    switch (dtype) {
+        case DAT_F32:
+            return launch_fwd<float>(word_ins_out, select_idx, is, selected_result, ss, row_stats, status, ex,
+                                     rows, prelen, slen, vocab, st, di, who);
+        case DAT_F16:
+            return launch_fwd<__half>(word_ins_out, select_idx, is, selected_result, ss, row_stats, status, ex,
+                                      rows, prelen, slen, vocab, st, di, who);
+        case DAT_BF16:
+            return launch_fwd<__nv_bfloat16>(word_ins_out, select_idx, is, selected_result, ss, row_stats,
+                                             status, ex, rows, prelen, slen, vocab, st, di, who);
+        default:
+            set_error("%s: unsupported dtype %d (fp32, fp16, bf16 only)", who, dtype);
+            return DAT_ERR_UNSUPPORTED;
+    }
+}
+
+static int gather_backward(void *word_ins_out, int dtype, const int64_t *select_idx, Strides3 is,
+                           const float *grad_selected, Strides3 gs, const float *row_stats,
+                           const int32_t *forced_step, int bsz, int prelen, int slen, int vocab,
+                           cudaStream_t st, const char *who) {
+    DAT_REQUIRE(bsz >= 0 && prelen >= 0 && slen >= 0 && vocab >= 1, DAT_ERR_BAD_ARG,
+                "%s: bad sizes bsz=%d prelen=%d slen=%d vocab=%d", who, bsz, prelen, slen, vocab);
+    if ((int64_t)bsz * prelen == 0) return DAT_OK;
+    DAT_REQUIRE(word_ins_out && row_stats && (slen == 0 || (select_idx && grad_selected)), DAT_ERR_BAD_ARG,
+                "%s: null pointer", who);
+    DAT_REQUIRE(slen <= 4096, DAT_ERR_UNSUPPORTED, "%s: slen=%d exceeds 4096", who, slen);
+    DeviceInfo di;
+    if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
+    const int64_t rows = (int64_t)bsz * prelen;
+    switch (dtype) {
+        case DAT_F32:
+            return launch_bwd<float>(word_ins_out, select_idx, is, grad_selected, gs, row_stats, forced_step,
+                                     rows, prelen, slen, vocab, st, di, who);
+        case DAT_F16:
+            return launch_bwd<__half>(word_ins_out, select_idx, is, grad_selected, gs, row_stats, forced_step,
+                                      rows, prelen, slen, vocab, st, di, who);
+        case DAT_BF16:
+            return launch_bwd<__nv_bfloat16>(word_ins_out, select_idx, is, grad_selected, gs, row_stats,
+                                             forced_step, rows, prelen, slen, vocab, st, di, who);
+        default:
+            set_error("%s: unsupported dtype %d", who, dtype);
+            return DAT_ERR_UNSUPPORTED;
+    }
 }
 
 }  // namespace dat
@@ -296,32 +497,34 @@ int dat_logsoftmax_gather(const void *word_ins_out, int dtype, const int64_t *se
                           int64_t sel_stride_s, float *row_stats, int32_t *status, int bsz,
                           int prelen, int slen, int vocab, void *stream) {
     using namespace dat;
-    DAT_REQUIRE(bsz >= 0 && prelen >= 0 && slen >= 0 && vocab >= 1, DAT_ERR_BAD_ARG,
-                "dat_logsoftmax_gather: bad sizes bsz=%d prelen=%d slen=%d vocab=%d", bsz, prelen,
-                slen, vocab);
-    if ((int64_t)bsz * prelen == 0) return DAT_OK;
-    DAT_REQUIRE(word_ins_out && (slen == 0 || (select_idx && selected_result)), DAT_ERR_BAD_ARG,
-                "dat_logsoftmax_gather: null pointer");
-    DeviceInfo di;
-    if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
-    const int64_t rows = (int64_t)bsz * prelen;
-    Strides3 is{idx_stride_b, idx_stride_l, idx_stride_s};
-    Strides3 ss{sel_stride_b, sel_stride_l, sel_stride_s};
+    const LsgExtras none{nullptr, nullptr, nullptr};
+    return gather_forward(word_ins_out, dtype, select_idx, Strides3{idx_stride_b, idx_stride_l, idx_stride_s},
+                          selected_result, Strides3{sel_stride_b, sel_stride_l, sel_stride_s}, row_stats,
+                          status, none, bsz, prelen, slen, vocab, static_cast<cudaStream_t>(stream),
+                          "dat_logsoftmax_gather");
+}
+
+int dat_logsoftmax_gather_fused(const void *word_ins_out, int dtype, const int64_t *select_idx,
+                                int64_t idx_stride_b, int64_t idx_stride_l, int64_t idx_stride_s,
+                                float *selected_result, int64_t sel_stride_b, int64_t sel_stride_l,
+                                int64_t sel_stride_s, float *row_stats, int64_t *argmax,
+                                const int64_t *force_emit, int32_t *forced_step, int32_t *status,
+                                int bsz, int prelen, int slen, int vocab, void *stream) {
+    using namespace dat;
+    const char *who = "dat_logsoftmax_gather_fused";
+    DAT_REQUIRE(!force_emit || forced_step, DAT_ERR_BAD_ARG,
+                "%s: force_emit needs the forced_step workspace [bsz, slen]", who);
+    DAT_REQUIRE(slen <= 8192, DAT_ERR_UNSUPPORTED, "%s: slen=%d exceeds 8192", who, slen);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    switch (dtype) {
-        case DAT_F32:
-            return launch_fwd<float>(word_ins_out, select_idx, is, selected_result, ss, row_stats,
-                                     status, rows, prelen, slen, vocab, st, di);
-        case DAT_F16:
-            return launch_fwd<__half>(word_ins_out, select_idx, is, selected_result, ss, row_stats,
-                                      status, rows, prelen, slen, vocab, st, di);
-        case DAT_BF16:
-            return launch_fwd<__nv_bfloat16>(word_ins_out, select_idx, is, selected_result, ss,
-                                             row_stats, status, rows, prelen, slen, vocab, st, di);
-        default:
-            set_error("dat_logsoftmax_gather: unsupported dtype %d (fp32, fp16, bf16 only)", dtype);
-            return DAT_ERR_UNSUPPORTED;
+    if (force_emit && (int64_t)bsz * prelen > 0 && slen > 0) {
+        lsg_forced_steps_kernel<<<(unsigned)bsz, 256, (size_t)slen * sizeof(int32_t), st>>>(
+            force_emit, forced_step, status, prelen, slen);
+        if (int rc = check_launch(who)) return rc;
     }
+    const LsgExtras ex{argmax, force_emit, force_emit ? forced_step : nullptr};
+    return gather_forward(word_ins_out, dtype, select_idx, Strides3{idx_stride_b, idx_stride_l, idx_stride_s},
+                          selected_result, Strides3{sel_stride_b, sel_stride_l, sel_stride_s}, row_stats,
+                          status, ex, bsz, prelen, slen, vocab, st, who);
 }
 
 int dat_logsoftmax_gather_backward(void *word_ins_out, int dtype, const int64_t *select_idx,
@@ -331,34 +534,23 @@ int dat_logsoftmax_gather_backward(void *word_ins_out, int dtype, const int64_t 
                                    const float *row_stats, int bsz, int prelen, int slen,
                                    int vocab, void *stream) {
     using namespace dat;
-    DAT_REQUIRE(bsz >= 0 && prelen >= 0 && slen >= 0 && vocab >= 1, DAT_ERR_BAD_ARG,
-                "dat_logsoftmax_gather_backward: bad sizes bsz=%d prelen=%d slen=%d vocab=%d", bsz,
-                prelen, slen, vocab);
-    if ((int64_t)bsz * prelen == 0) return DAT_OK;
-    DAT_REQUIRE(word_ins_out && row_stats && (slen == 0 || (select_idx && grad_selected)),
-                DAT_ERR_BAD_ARG, "dat_logsoftmax_gather_backward: null pointer");
-    DAT_REQUIRE(slen <= 4096, DAT_ERR_UNSUPPORTED,
-                "dat_logsoftmax_gather_backward: slen=%d exceeds 4096", slen);
-    DeviceInfo di;
-    if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
-    const int64_t rows = (int64_t)bsz * prelen;
-    Strides3 is{idx_stride_b, idx_stride_l, idx_stride_s};
-    Strides3 gs{g_stride_b, g_stride_l, g_stride_s};
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    switch (dtype) {
-        case DAT_F32:
-            return launch_bwd<float>(word_ins_out, select_idx, is, grad_selected, gs, row_stats,
-                                     rows, prelen, slen, vocab, st, di);
-        case DAT_F16:
-            return launch_bwd<__half>(word_ins_out, select_idx, is, grad_selected, gs, row_stats,
-                                      rows, prelen, slen, vocab, st, di);
-        case DAT_BF16:
-            return launch_bwd<__nv_bfloat16>(word_ins_out, select_idx, is, grad_selected, gs,
-                                             row_stats, rows, prelen, slen, vocab, st, di);
-        default:
-            set_error("dat_logsoftmax_gather_backward: unsupported dtype %d", dtype);
-            return DAT_ERR_UNSUPPORTED;
-    }
+    return gather_backward(word_ins_out, dtype, select_idx, Strides3{idx_stride_b, idx_stride_l, idx_stride_s},
+                           grad_selected, Strides3{g_stride_b, g_stride_l, g_stride_s}, row_stats, nullptr,
+                           bsz, prelen, slen, vocab, static_cast<cudaStream_t>(stream),
+                           "dat_logsoftmax_gather_backward");
+}
+
+int dat_logsoftmax_gather_backward_fused(void *word_ins_out, int dtype, const int64_t *select_idx,
+                                         int64_t idx_stride_b, int64_t idx_stride_l,
+                                         int64_t idx_stride_s, const float *grad_selected,
+                                         int64_t g_stride_b, int64_t g_stride_l, int64_t g_stride_s,
+                                         const float *row_stats, const int32_t *forced_step, int bsz,
+                                         int prelen, int slen, int vocab, void *stream) {
+    using namespace dat;
+    return gather_backward(word_ins_out, dtype, select_idx, Strides3{idx_stride_b, idx_stride_l, idx_stride_s},
+                           grad_selected, Strides3{g_stride_b, g_stride_l, g_stride_s}, row_stats, forced_step,
+                           bsz, prelen, slen, vocab, static_cast<cudaStream_t>(stream),
+                           "dat_logsoftmax_gather_backward_fused");
 }
 
 }  // extern "C"

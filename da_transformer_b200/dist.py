@@ -25,6 +25,9 @@ def sentence_stats(loss_result: torch.Tensor, target_length: torch.Tensor) -> to
 
     Mirrors fs_plugins/criterions/nat_dag_loss.py:190-194: sentences whose
     log-likelihood is inf/nan are zeroed and counted as invalid.  No host sync.
+    The result is detached on every device: these are the LOGGING statistics that get
+    all-reduced, not a differentiable loss (``criterion_glue.dag_loss_mean`` is the
+    differentiable reduction).
     On the GPU this is one launch of the library (``dat_sentence_stats``) instead of a dozen
     elementwise and reduction launches; CPU tensors (the gloo tests of the multi-process glue)
     take the same expression in torch ops."""
@@ -37,6 +40,7 @@ def sentence_stats(loss_result: torch.Tensor, target_length: torch.Tensor) -> to
             _native.ptr(loss32), _native.ptr(tl64), _native.ptr(stats), int(loss32.numel()),
             _native.stream_ptr(loss_result.device)), "dat_sentence_stats")
         return stats
+    loss_result = loss_result.detach()
     invalid = loss_result.isinf().logical_or(loss_result.isnan())
     clean = loss_result.masked_fill(invalid, 0).to(torch.float64)
     tl = target_length.to(torch.float64)

@@ -52,7 +52,7 @@ def band_to_square(band: torch.Tensor) -> torch.Tensor:
 
 
 def make_links(B: int, L: int, output_length: torch.Tensor, gen: torch.Generator,
-               translen: Optional[int] = None, chunk: int = 64) -> torch.Tensor:
+               translen: Optional[int] = None, chunk: int = 64, score_scale: float = 1.0) -> torch.Tensor:
     """Band links [B,L,K] fp32: row-wise log_softmax of N(0,1) scores over the valid
     successors (j > i, both below output_length); rows without a successor are all
     -inf (a bare log_softmax would give NaN there; the model writes -inf too,
@@ -63,6 +63,8 @@ def make_links(B: int, L: int, output_length: torch.Tensor, gen: torch.Generator
         e = min(B, s + chunk)
         ol = output_length[s:e].view(-1, 1, 1)
         scores = torch.randn(e - s, L, L, generator=gen, dtype=torch.float32)
+        if score_scale != 1.0:
+            scores = scores * score_scale
         valid = (ar.view(1, 1, L) > ar.view(1, L, 1)) & (ar.view(1, 1, L) < ol) & (ar.view(1, L, 1) < ol)
         scores = scores.masked_fill(~valid, NEG_INF)
         has = valid.any(-1, keepdim=True)
@@ -201,6 +203,27 @@ def config4(gen=None, B=512, L=512, V=42000, tl_lo=32, tl_hi=64) -> DagBatch:
     links = make_links(B, L, ol, gen)
     match = synthetic_match(B, T, L, V, 2.0, gen)
     return DagBatch("C4", None, targets, links, ol, tl, match)
+
+
+def config4_peaky(gen=None, B=512, L=512, V=42000, tl_lo=32, tl_hi=64, score_scale=8.0) -> DagBatch:
+    """C4 shapes with the value distribution of a TRAINED graph instead of a random one: transition
+    scores N(0, score_scale) before the row softmax (a few successors carry almost all the mass), and
+    match rows in which one vertex per target token is near probability one (log-prob -0.2) while
+    the others sit near -15 +- 3 nats.  The dominant vertices increase with the target step and
+    start / end on the first / last vertex, so every sentence keeps a likely path."""
+    gen = gen or generator(40)
+    tl = torch.randint(tl_lo, tl_hi + 1, (B,), generator=gen, dtype=torch.int64)
+    T = tl_hi
+    ol = torch.full((B,), L, dtype=torch.int64)
+    targets = _targets(B, T, tl, V, gen)
+    links = make_links(B, L, ol, gen, score_scale=score_scale)
+    match = torch.randn(B, T, L, generator=gen, dtype=torch.float32) * 3.0 - 15.0
+    for b in range(B):
+        n = int(tl[b])
+        inner = torch.sort(torch.randperm(L - 2, generator=gen)[: n - 2] + 1).values
+        pos = torch.cat([torch.zeros(1, dtype=torch.long), inner, torch.full((1,), L - 1, dtype=torch.long)])
+        match[b, torch.arange(n), pos] = -0.2
+    return DagBatch("C4-peaky", None, targets, links, ol, tl, match)
 
 
 def small_batch(seed=0, B=4, L=24, T=6, V=50, translen=None, ragged=True,

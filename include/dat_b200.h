@@ -96,6 +96,39 @@ int dat_logsoftmax_gather_backward(void *word_ins_out, int dtype,
                                    int bsz, int prelen, int slen, int vocab, void *stream);
 
 /*
+ * dat_logsoftmax_gather with two pieces of the criterion's glue done in the same pass over the
+ * logits (what surrounds the call at fs_plugins/criterions/nat_dag_loss.py:246-262 and 166-179):
+ *   argmax (optional, [bsz*prelen] int64): word_ins_out.argmax(-1), the glancing sampler's
+ *     prediction (nat_dag_loss.py:246), with torch.argmax's result on ties (first index) and NaN;
+ *   force_emit (optional, [bsz,prelen] int64 contiguous, -1 = free): the forced alignment of
+ *     NATDAGLoss._force_aligment (nat_dag_loss.py:111-120) applied to the gathered values, which
+ *     must then be the match matrix (slen = tarlen, select_idx = the target tokens): for every
+ *     target step s that some vertex of the sentence is forced to emit, selected_result[b,l,s] is 0
+ *     at the forced vertex and -inf elsewhere.  forced_step ([bsz,slen] int32, written here) marks
+ *     those steps; dat_logsoftmax_gather_backward_fused takes it to stop the gradient there, as the
+ *     reference's masked_fill does.  A forced step >= slen sets DAT_STATUS_BAD_INDEX.
+ * slen <= 8192 when force_emit is given.
+ */
+int dat_logsoftmax_gather_fused(const void *word_ins_out, int dtype,
+                                const int64_t *select_idx, int64_t idx_stride_b, int64_t idx_stride_l,
+                                int64_t idx_stride_s,
+                                float *selected_result, int64_t sel_stride_b, int64_t sel_stride_l,
+                                int64_t sel_stride_s,
+                                float *row_stats, int64_t *argmax, const int64_t *force_emit,
+                                int32_t *forced_step, int32_t *status,
+                                int bsz, int prelen, int slen, int vocab, void *stream);
+
+/* dat_logsoftmax_gather_backward for a forward done with force_emit: gradients arriving at the
+ * forced steps (forced_step[b,s] != 0) are dropped (nat_dag_loss.py:117).  forced_step may be NULL. */
+int dat_logsoftmax_gather_backward_fused(void *word_ins_out, int dtype,
+                                         const int64_t *select_idx, int64_t idx_stride_b,
+                                         int64_t idx_stride_l, int64_t idx_stride_s,
+                                         const float *grad_selected, int64_t g_stride_b,
+                                         int64_t g_stride_l, int64_t g_stride_s,
+                                         const float *row_stats, const int32_t *forced_step,
+                                         int bsz, int prelen, int slen, int vocab, void *stream);
+
+/*
  * Replaces `dag_loss` (dag_loss.cpp:19; dag_loss.cu:313-375).
  * Runs the alpha recursion and, if require_gradient, the beta recursion, and writes
  * loss[b] = log P(target | graph) (beta[b,0,0] when require_gradient, else
@@ -131,6 +164,12 @@ int dat_dag_loss_fast(const float *match_all, const float *links, const int64_t 
                       const int64_t *target_length, float *alpha, float *beta, double *offsets,
                       float *loss, int32_t *status, void *scratch,
                       int bsz, int tarlen, int prelen, int translen, void *stream);
+
+/* Number of sentences of the last dat_dag_loss_fast call on `scratch` that its dynamic-range check
+ * handed to the exact kernels, written to the device word *count (no counterpart in the reference;
+ * it is what the status bit DAT_STATUS_FAST_FALLBACK summarises). */
+int dat_dag_loss_fast_flagged(const void *scratch, int32_t *count, int bsz, int tarlen, int prelen,
+                              void *stream);
 
 /*
  * Backward for a forward done by dat_dag_loss_fast (replaces dag_loss_backward, dag_loss.cpp:20;
@@ -198,14 +237,6 @@ int dat_dag_best_alignment(const float *match_all, const float *links,
                            void *stream);
 
 /*
- * Measurement helper, no counterpart in the reference: launches `blocks` CTAs of 1024
- * threads that each execute 8*iters dependent-chain ex2 evaluations per thread, so that
- * blocks*1024*8*iters / elapsed is the device's sustained special-function rate (the
- * roofline denominator of the DAG recursion kernels).  `sink` is one device float.
- */
-int dat_probe_mufu(int iters, int blocks, float *sink, void *stream);
-
-/*
  * Per-shard statistics of the criterion in one launch (replaces the elementwise and reduction
  * launches of fs_plugins/criterions/nat_dag_loss.py:190-194 that follow dag_loss, and produces the
  * fp64 buffer the reference all-reduces, fairseq/distributed/utils.py:634-680):
@@ -215,6 +246,74 @@ int dat_probe_mufu(int iters, int blocks, float *sink, void *stream);
  */
 int dat_sentence_stats(const float *loss, const int64_t *target_length, double *stats, int bsz,
                        void *stream);
+
+/*
+ * dat_sentence_stats plus the criterion's differentiable scalar (nat_dag_loss.py:190-194) in the same
+ * launch: *mean_out = -(1/bsz) * sum_b clean_b / target_length_b (inf/nan sentences zeroed), and
+ * grad_scale[b] = d mean / d loss_b = -1 / (target_length_b * bsz), 0 for the zeroed sentences.
+ * mean_out: one device float; grad_scale: [bsz] fp32.
+ */
+int dat_sentence_mean(const float *loss, const int64_t *target_length, double *stats, float *mean_out,
+                      float *grad_scale, int bsz, void *stream);
+
+/*
+ * Replaces the tail of GlatDecomposedLink.extract_links
+ * (fs_plugins/models/glat_decomposed_with_link.py:380-404 with extract_valid_links :319-335): from the
+ * per-head transition scores and the per-vertex head log-probabilities to the band links dag_loss
+ * reads, without the [B,L,K,H] intermediates of the reference.
+ *   content   [bsz,prelen,prelen,heads] fp32 contiguous   log_multi_content (q.k / sqrt(d) per head)
+ *   log_gates [bsz,prelen,heads] fp32                     log_softmax of the gate scores
+ *   links[b,i,d] = logsumexp_h( log_softmax over the valid successors j of content[b,i,j,h] + log_gates[b,i,h] )
+ *                  with j = i+d+1; -inf where j is not a valid successor and for vertices without one.
+ * Valid successors of i: i < j <= min(prelen-1, i+translen), and j <= bound_end[b,i] when bound_end
+ * ([bsz,prelen] int64, the decoding mask, :390-393) is given, and nonpad[b,j] != 0 when nonpad
+ * ([bsz,prelen] uint8, prev_output_tokens != pad, the training mask, :394-395) is given; either may be NULL.
+ * head_lse (optional output, [bsz,prelen,heads] fp32): the per-head log-sum-exp the backward needs.
+ * heads <= 256; (prelen-1)*heads*4 bytes must fit in shared memory (about 220 KB).
+ */
+int dat_links_from_heads(const float *content, const float *log_gates, const int64_t *bound_end,
+                         const unsigned char *nonpad, float *links, float *head_lse,
+                         int bsz, int prelen, int heads, int translen, void *stream);
+
+/*
+ * Gradient of dat_links_from_heads (the reference differentiates :380-404 by autograd).
+ * grad_content [bsz,prelen,prelen,heads] is written completely (zeros outside the valid successors)
+ * and may alias content; grad_log_gates [bsz,prelen,heads].  links / head_lse: the forward's outputs.
+ */
+int dat_links_from_heads_backward(const float *grad_links, const float *content, const float *log_gates,
+                                  const float *links, const float *head_lse, const int64_t *bound_end,
+                                  const unsigned char *nonpad, float *grad_content, float *grad_log_gates,
+                                  int bsz, int prelen, int heads, int translen, void *stream);
+
+/*
+ * Node-passing probabilities of GlatDecomposedLink._analyze_graph
+ * (fs_plugins/models/glat_decomposed_with_link.py:559-569): node_pass[b,j] = probability that a path
+ * starting at vertex 0 visits vertex j.  links_square [bsz,prelen,prelen] fp32 holds log P(i -> j) and
+ * must be -inf on and below the diagonal (what restore_valid_links produces, :337-349).
+ */
+int dat_node_passing_prob(const float *links_square, float *node_pass, int bsz, int prelen, void *stream);
+
+/*
+ * Replaces GlatDecomposedLink.inference_viterbi (fs_plugins/models/glat_decomposed_with_link.py:720-777).
+ *   links_square     [bsz,prelen,prelen] fp32  log P(i -> j)  (only read; the reference adds the token
+ *                    scores into row 0 in place, :727-732, which changes no result while links[0][0] = -inf)
+ *   unreduced_logits [bsz,prelen] fp32, unreduced_tokens [bsz,prelen] int64: max and arg-max over the
+ *                    vocabulary of the normalised logits (:721)
+ *   joint            != 0 for decode_strategy "jointviterbi" (token scores join every step)
+ *   max_length       number of lengths tried (the reference uses 2 * prelen / upsample_scale, :735)
+ *   beta             exponent of the length penalty (decode_viterbibeta, :753)
+ * Outputs: out_tokens [bsz,max_length] int64, the collapsed token sequence padded with pad_index
+ * (repeated and pad tokens dropped as in :762-769); out_length [bsz] its length; out_vertices
+ * [bsz,max_length] the vertices of the best path before the collapse (-1 padded); out_score [bsz] the
+ * length-normalised score.  Maxima resolve ties to the first index like torch.max.
+ * workspace: dat_viterbi_decode_workspace_bytes(...) bytes (the back-pointers).
+ */
+size_t dat_viterbi_decode_workspace_bytes(int bsz, int prelen, int max_length);
+int dat_viterbi_decode(const float *links_square, const float *unreduced_logits,
+                       const int64_t *unreduced_tokens, const int64_t *output_length, void *workspace,
+                       int64_t *out_tokens, int64_t *out_length, int64_t *out_vertices, float *out_score,
+                       int32_t *status, int bsz, int prelen, int max_length, int joint, float beta,
+                       int64_t pad_index, void *stream);
 
 #ifdef __cplusplus
 }

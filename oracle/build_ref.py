@@ -42,5 +42,7 @@ def build(reference):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get(
+        "DAT_REFERENCE_DIR", os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")),
+        help="DA-Transformer checkout (default: $DAT_REFERENCE_DIR, else ../reference)")
     sys.exit(build(ap.parse_args().reference))

@@ -8,7 +8,10 @@
  * Parity pin: this restatement is checked against golden vectors produced by
  * importing the reference's own torch-native functions (torch_dag_loss,
  * torch_dag_best_alignment, torch_dag_logsoftmax_gather_inplace of
- * fs_plugins/custom_ops/dag_loss.py:259-359) — see tests/golden/make_golden.py.
+ * fs_plugins/custom_ops/dag_loss.py:259-359) — see tests/golden/make_golden.py — and, for
+ * the functions of graph_oracle_impl.inc (forced alignment, extract_links tail, decode-side
+ * dynamic programmes), by running the reference's own method bodies — see
+ * tests/golden/make_golden_graph.py.
  * The reference has no golden vectors of its own, and the reduction order of its
  * CUDA kernels is not pinned by any reference test, so bit-level parity of the
  * floating-point results is unpinned; they are pinned to tolerances.  The
@@ -17,6 +20,7 @@
  * Build: see oracle/Makefile  (gcc -O2 -fopenmp -shared -fPIC).
  */
 #include <math.h>
+#include <omp.h>
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -26,6 +30,7 @@
 #define EXP exp
 #define LOG log
 #include "dag_oracle_impl.inc"
+#include "graph_oracle_impl.inc"
 #undef REAL
 #undef SFX
 #undef EXP
@@ -36,6 +41,7 @@
 #define EXP expf
 #define LOG logf
 #include "dag_oracle_impl.inc"
+#include "graph_oracle_impl.inc"
 #undef REAL
 #undef SFX
 #undef EXP
@@ -64,4 +70,11 @@ void oracle_square_to_band_f64(const double *sq, int B, int L, int K, double *ba
             }
 }
 
-int oracle_abi_version(void) { return 1; }
+int oracle_abi_version(void) { return 2; }
+
+/* Number of OpenMP threads the parallel loops will use; n > 0 sets it first (launchers such as
+ * torchrun export OMP_NUM_THREADS=1, which would silently make a "32 thread" baseline single-threaded). */
+int oracle_set_threads(int n) {
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+}

@@ -21,7 +21,7 @@ _lib = None
 
 def build(force=False):
     """Compile oracle/dag_oracle.c -> oracle/liboracle.so (gcc, OpenMP)."""
-    src = [os.path.join(_HERE, f) for f in ("dag_oracle.c", "dag_oracle_impl.inc")]
+    src = [os.path.join(_HERE, f) for f in ("dag_oracle.c", "dag_oracle_impl.inc", "graph_oracle_impl.inc")]
     if not force and os.path.exists(_LIB_PATH):
         if all(os.path.getmtime(_LIB_PATH) >= os.path.getmtime(s) for s in src):
             return _LIB_PATH
@@ -36,6 +36,11 @@ def lib():
         build()
         _lib = ctypes.CDLL(_LIB_PATH)
     return _lib
+
+
+def set_threads(n=0):
+    """Sets (n > 0) and returns the number of OpenMP threads the oracle's loops use."""
+    return int(lib().oracle_set_threads(int(n)))
 
 
 def _sfx(dtype):
@@ -183,3 +188,81 @@ def square_to_band(sq, K=None):
     band = np.empty((B, L, K), dtype=np.float64)
     lib().oracle_square_to_band_f64(_p(sq), B, L, K, _p(band))
     return band
+
+
+def force_alignment(match_all, force_emit, dtype=np.float64):
+    """NATDAGLoss._force_aligment (nat_dag_loss.py:111-120) on match_all [B,T,L] with force_emit
+    [B,L] (-1 = free).  Returns a new array."""
+    sfx, _ = _sfx(dtype)
+    m = np.array(match_all, dtype=dtype, order="C", copy=True)
+    fe = np.ascontiguousarray(np.asarray(force_emit), dtype=np.int64)
+    B, T, L = m.shape
+    getattr(lib(), "oracle_force_alignment" + sfx)(_p(m), _p(fe), B, T, L)
+    return m
+
+
+def _masks(bound_end, nonpad, B, L):
+    be = None if bound_end is None else np.ascontiguousarray(np.asarray(bound_end), dtype=np.int64)
+    npd = None if nonpad is None else np.ascontiguousarray(np.asarray(nonpad), dtype=np.uint8)
+    assert be is None or be.shape == (B, L)
+    assert npd is None or npd.shape == (B, L)
+    return be, npd
+
+
+def links_from_heads(content, log_gates, K, bound_end=None, nonpad=None, dtype=np.float64):
+    """Tail of extract_links (glat_decomposed_with_link.py:399-404): content [B,L,L,H], log_gates
+    [B,L,H] -> band links [B,L,K] and the per-head normaliser [B,L,H]."""
+    sfx, _ = _sfx(dtype)
+    content, log_gates = _prep(dtype, content, log_gates)
+    B, L, _, H = content.shape
+    be, npd = _masks(bound_end, nonpad, B, L)
+    links = np.empty((B, L, K), dtype=dtype)
+    lse = np.empty((B, L, H), dtype=dtype)
+    getattr(lib(), "oracle_links_from_heads" + sfx)(
+        _p(content), _p(log_gates), None if be is None else _p(be), None if npd is None else _p(npd),
+        B, L, H, int(K), _p(links), _p(lse))
+    return links, lse
+
+
+def links_from_heads_backward(grad_links, content, log_gates, K, bound_end=None, nonpad=None,
+                              dtype=np.float64):
+    """Gradient of links_from_heads with respect to (content, log_gates)."""
+    sfx, _ = _sfx(dtype)
+    grad_links, content, log_gates = _prep(dtype, grad_links, content, log_gates)
+    B, L, _, H = content.shape
+    be, npd = _masks(bound_end, nonpad, B, L)
+    gc = np.empty_like(content)
+    gg = np.empty_like(log_gates)
+    getattr(lib(), "oracle_links_from_heads_backward" + sfx)(
+        _p(grad_links), _p(content), _p(log_gates), None if be is None else _p(be),
+        None if npd is None else _p(npd), B, L, H, int(K), _p(gc), _p(gg))
+    return gc, gg
+
+
+def node_passing_prob(links_square, dtype=np.float64):
+    """_analyze_graph's node-passing probabilities (glat_decomposed_with_link.py:559-569), [B,L]."""
+    sfx, _ = _sfx(dtype)
+    (lk,) = _prep(dtype, links_square)
+    B, L, _ = lk.shape
+    out = np.empty((B, L), dtype=dtype)
+    getattr(lib(), "oracle_node_passing_prob" + sfx)(_p(lk), B, L, _p(out))
+    return out
+
+
+def viterbi_decode(links_square, unreduced_logits, unreduced_tokens, output_length, max_length,
+                   joint=False, beta=1.0, pad=1, dtype=np.float32):
+    """inference_viterbi (glat_decomposed_with_link.py:720-777).  Returns (tokens [B,max_length],
+    lengths [B], vertices [B,max_length], scores [B])."""
+    sfx, ctype = _sfx(dtype)
+    lk, lg = _prep(dtype, links_square, unreduced_logits)
+    tk = np.ascontiguousarray(np.asarray(unreduced_tokens), dtype=np.int64)
+    ol = np.ascontiguousarray(np.asarray(output_length), dtype=np.int64)
+    B, L, _ = lk.shape
+    toks = np.empty((B, max_length), dtype=np.int64)
+    verts = np.empty((B, max_length), dtype=np.int64)
+    lens = np.empty(B, dtype=np.int64)
+    score = np.empty(B, dtype=dtype)
+    getattr(lib(), "oracle_viterbi_decode" + sfx)(
+        _p(lk), _p(lg), _p(tk), _p(ol), B, L, int(max_length), int(bool(joint)), ctype(beta),
+        ctypes.c_int64(pad), _p(toks), _p(lens), _p(verts), _p(score))
+    return toks, lens, verts, score

@@ -111,7 +111,8 @@ def config0_case(ref):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get(
+        "DAT_REFERENCE_DIR", os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference")))
     args = ap.parse_args()
     ref = load_reference(args.reference)
     torch.manual_seed(0)

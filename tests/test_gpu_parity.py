@@ -11,7 +11,7 @@ import torch
 from oracle import oracle
 from da_transformer_b200 import (DagBestAlignmentFunc, DagLogsoftmaxGatherFunc, DagLossFunc, dag_best_alignment,
                                  dag_logsoftmax_gather_inplace, dag_loss, last_status, workloads)
-from util import assert_rel, assert_rel_quantized, golden
+from util import assert_rel, assert_rel_per_sentence, assert_rel_quantized, golden
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -49,6 +49,8 @@ def check_dag_against_oracle(batch, grad_out=None):
     assert_rel(loss_ng, rl, TOL_LOSS, "loss (alpha, no grad)")
     assert_rel(gm, rgm, TOL_GRAD, "grad_match")
     assert_rel(gl, rgl, TOL_GRAD, "grad_links")
+    assert_rel_per_sentence(gm, rgm, TOL_GRAD, "grad_match")
+    assert_rel_per_sentence(gl, rgl, TOL_GRAD, "grad_links")
 
 
 @pytest.mark.parametrize("seed,B,L,T,K", [
@@ -57,6 +59,8 @@ def check_dag_against_oracle(batch, grad_out=None):
     # more than 64 target steps with all rows still in shared memory (strip sweep, two passes of its
     # matrix-product phase), full and banded links
     (9, 2, 190, 100, None), (10, 2, 190, 100, 40),
+    # graphs longer than 1024 vertices (a thread of the exact alpha sweep then finalises more than two columns)
+    (11, 2, 1300, 12, None), (12, 1, 2048, 6, 700),
 ])
 def test_dag_loss_matches_oracle(seed, B, L, T, K):
     batch = workloads.small_batch(seed=seed, B=B, L=L, T=T, V=50, translen=K)
@@ -98,6 +102,7 @@ def test_forced_alignment_match_with_minus_inf_and_zero():
 @pytest.mark.parametrize("seed,B,L,T,K,quant", [
     (1, 5, 24, 6, None, 0), (2, 4, 40, 9, 6, 0), (3, 4, 70, 12, None, 0.5), (4, 3, 97, 13, 20, 1.0),
     (5, 2, 160, 20, None, 0.25), (6, 2, 64, 5, None, 2.0), (7, 2, 190, 100, None, 0.5), (8, 2, 190, 100, 40, 0.5),
+    (9, 1, 1300, 12, None, 0.5),
 ])
 def test_best_alignment_bit_exact(config, seed, B, L, T, K, quant):
     batch = workloads.small_batch(seed=seed, B=B, L=L, T=T, V=50, translen=K)
@@ -171,8 +176,9 @@ def test_gather_matches_oracle(dtype, tol, B, L, V, S, transposed):
         assert_rel(dx.numpy(), ref_dx, tol, "dlogits")
     else:
         assert_rel_quantized(dx.float().numpy(), ref_dx, tol, str(dtype).replace("torch.", ""), "dlogits")
-        if dtype == torch.float16:   # fp16's rounding fits inside the budget as it is
-            assert_rel(dx.float().numpy(), ref_dx, tol, "dlogits")
+        # the plain rule as well: one rounding of the largest element costs at most 2^-9 = 1.95e-3 of it
+        # in bf16 (2^-12 in fp16), and smaller elements cost less in absolute terms
+        assert_rel(dx.float().numpy(), ref_dx, tol, "dlogits")
 
 
 @pytest.mark.parametrize("name,tol", [("gather_small_f32", TOL_GRAD), ("gather_small_f16", TOL_GRAD_HALF),
@@ -188,6 +194,7 @@ def test_gather_matches_reference_golden(name, tol):
     else:
         name16 = str(dtype).replace("torch.", "")
         assert_rel_quantized(dx.float().numpy(), g["dlogits_f64"], tol, name16, "dlogits vs fp64")
+        assert_rel(dx.float().numpy(), g["dlogits_f64"], tol, "dlogits vs fp64, plain rule")
         # both round the same fp32 value once: they may differ by one unit in the last place
         ulp = 2.0 ** (np.floor(np.log2(np.maximum(np.abs(g["dlogits"]), 1e-30))) - (10 if dtype == torch.float16 else 7))
         assert (np.abs(dx.float().numpy() - g["dlogits"]) <= ulp + 1e-12).all()

@@ -32,6 +32,31 @@ def assert_rel(actual, ref, tol, what=""):
     return e
 
 
+def assert_rel_per_sentence(actual, ref, tol, what="", rtol_big=1e-3, big=1e-6):
+    """The tolerance applied to every sentence (leading index) on its own scale, so that a
+    sentence with small gradients cannot hide behind a large one; and, on top, every entry
+    above `big` times its sentence's maximum must be right to `rtol_big` relative to itself
+    (catches entries flushed or truncated by a path that rescales)."""
+    actual = np.asarray(actual, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    assert actual.shape == ref.shape, (actual.shape, ref.shape)
+    worst = 0.0
+    for b in range(ref.shape[0]):
+        e = rel_err(actual[b], ref[b])
+        assert e <= tol, f"{what}, sentence {b}: max|d|/max|ref| = {e:.3e} > {tol:.1e}"
+        worst = max(worst, e)
+        r = ref[b]
+        fin = np.isfinite(r)
+        if fin.any():
+            scale = np.abs(r[fin]).max()
+            sel = fin & (np.abs(r) > big * scale)
+            if sel.any():
+                rel = np.abs(actual[b][sel] - r[sel]) / np.abs(r[sel])
+                assert rel.max() <= rtol_big, (f"{what}, sentence {b}: an entry above {big:g} of the sentence "
+                                               f"maximum is off by {rel.max():.3e} of itself")
+    return worst
+
+
 _PRECISION_BITS = {"float16": 11, "bfloat16": 8}
 
 
