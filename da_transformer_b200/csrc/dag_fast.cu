@@ -18,7 +18,7 @@
 //
 // What it costs: dynamic range.  A row is rescaled so that its maximum sits near 2^37..2^64;
 // anything below 2^-126 (2^-149 with denormals) in those units is flushed.  Sentences that
-// contain a finite link or an in-window match below 2^-100 are sent to the exact kernel up
+// contain a finite link or an in-window match below 2^-120 are sent to the exact kernel up
 // front (their exp() would flush by itself), so what can be lost is a quantity below 2^-150
 // of its row's maximum, and the likelihood mass it could carry is bounded by
 //     2^-150 * max_j alpha_t[j] * max_j betahat_t[j]      (betahat = beta without match)
@@ -39,8 +39,16 @@ namespace dat {
 constexpr int kFastThreads = 512;
 constexpr int kFastWarps = kFastThreads / 32;
 constexpr int kTargetExp = 64;   // rows are rescaled with 2^-(floor(log2 max) - kTargetExp)
-constexpr float kMaxSpread = 100.f;
-constexpr float kMinLog2Input = -100.f;  // finite links / matches below this go to the exact kernel
+constexpr float kMaxSpread = 100.f;        // row-wide spread (bits) a sentence may have when the flush is row-relative
+constexpr float kMaxSpreadLocal = 140.f;   // spread inside a 32-vertex sub-strip (the flush there is 2^-190 relative)
+constexpr float kMaxSpreadBackward = 200.f;   // row-wide spread up to which grad_links may use the product form
+constexpr float kMinLog2Input = -120.f;  // finite links / matches below this go to the exact kernel
+// Per-sentence word in the scratch.  The sweeps OR in what they saw; dag_fast_check_kernel turns it
+// into the verdict the later launches read.
+constexpr int kFlagTiny = 1;            // in: a finite link or in-window match below 2^kMinLog2Input
+constexpr int kFlagHole = 4;            // in: two vertices of the graph without a (finite) link between them
+constexpr int kFlagRedo = 1;            // out: forward and backward by the exact log-domain kernels
+constexpr int kFlagExactBackward = 2;   // out: forward kept, grad_links by the exact kernel
 
 }  // namespace dat
 #include "dag_strip.cuh"
@@ -50,18 +58,25 @@ __host__ __device__ inline int fast_pitch(int L) { return (L + 127) & ~127; }
 __host__ __device__ inline int fast_rows(int L) { return (L + 15) & ~15; }
 
 struct FastScratch {
-    float *esq;   // [B][rows][pitch]   E = exp(links), square layout, zero padded
+    float *esq;   // [B][rows][pitch]   E = exp(links), square layout, zero padded (tiled path only)
     float *chk;   // [B][2][T]          log2 row maxima: alpha rows, betahat rows
-    int *flag;    // [B]                1 = recompute with the exact kernel
+    float *sub;   // [B][2][T][nH]      the same per 32-vertex sub-strip (strip path only)
+    int *flag;    // [B]                kFlag* bits, then the verdict
     int *order;   // [B]                sentences sorted by decreasing cost
 };
+
+__host__ __device__ inline int strip_row_pitch_hd(int prelen) { return ((prelen + 63) & ~63) + 4; }
+__host__ __device__ inline int fast_sub_strips(int L) { return strip_row_pitch_hd(L) / 32; }
+
 
 // the square matrix comes last so that a caller that does not need it (strip sweep) can leave it out
 __host__ __device__ inline size_t fast_scratch_bytes(int B, int T, int L, bool with_esq) {
     size_t e = with_esq ? (size_t)B * fast_rows(L) * fast_pitch(L) * sizeof(float) : 0;
     size_t c = (size_t)B * 2 * T * sizeof(float);
     size_t f = (size_t)B * sizeof(int) * 2;
-    return ((e + 255) & ~(size_t)255) + ((c + 255) & ~(size_t)255) + ((f + 255) & ~(size_t)255) + 256;
+    size_t u = (size_t)B * 2 * T * fast_sub_strips(L) * sizeof(float);
+    return ((e + 255) & ~(size_t)255) + ((c + 255) & ~(size_t)255) + ((f + 255) & ~(size_t)255) +
+           ((u + 255) & ~(size_t)255) + 256;
 }
 
 static inline FastScratch carve_fast(void *scratch, int B, int T, int L) {
@@ -72,6 +87,8 @@ static inline FastScratch carve_fast(void *scratch, int B, int T, int L) {
     s.flag = reinterpret_cast<int *>(p);
     s.order = s.flag + B;
     p += (((size_t)B * sizeof(int) * 2) + 255) & ~(size_t)255;
+    s.sub = reinterpret_cast<float *>(p);
+    p += (((size_t)B * 2 * T * fast_sub_strips(L) * sizeof(float)) + 255) & ~(size_t)255;
     s.esq = reinterpret_cast<float *>(p);   // only present (and only touched) on the tiled path
     return s;
 }
@@ -420,21 +437,41 @@ dag_fast_sweep_kernel(const float *__restrict__ match_all, const float *__restri
     }
 }
 
-// One thread per sentence: flag = 1 unless the likelihood is finite and, at every step, the
-// product of the best prefix mass and the best suffix mass is within 2^kMaxSpread of it.
+// One warp per sentence: the verdict on what the probability-domain sweeps left behind.
+// What they can lose is what underflowed in the unit it was added in.  Two bounds cover it:
+//  * everything is within 2^-190 of the largest entry of its own 32-vertex sub-strip at that step
+//    (rows, in-group sums), so with R_sub = max over (t, sub-strip) of
+//        log2(max_{j in sub-strip} alpha_t[j] * max_{j in sub-strip} betahat_t[j] / Z) <= kMaxSpreadLocal
+//    a lost quantity could have carried at most 2^(-190 + kMaxSpreadLocal) = 2^-50 of the likelihood;
+//  * what finished vertex groups send forward is scaled to ONE unit per step, the largest entry of the
+//    finished vertices.  An entry 2^-190 below that unit vanishes.  If every pair of vertices is
+//    linked with a probability above 2^kMinLog2Input (no hole, nothing tiny), the largest finished
+//    entry itself reaches every later vertex with at least 2^kMinLog2Input of its size, so what
+//    vanished is below 2^(-190 - kMinLog2Input) = 2^-70 of what arrived.  With holes in the graph
+//    that argument fails and the row-wide spread R_t = log2(max alpha_t * max betahat_t / Z) must
+//    stay below kMaxSpread instead (the tiled sweep, whose rows have a single unit, always needs that).
+// The product form of grad_links multiplies factors of size 2^(R_t / 2); beyond kMaxSpreadBackward its
+// factors would underflow where they matter, so those sentences get the exact grad_links kernel.
 __global__ void dag_fast_check_kernel(const double *__restrict__ offsets_all, const float *__restrict__ chk_all,
+                                      const float *__restrict__ sub_all, int nH,
                                       const int64_t *__restrict__ output_length,
                                       const int64_t *__restrict__ target_length, int *__restrict__ flag,
                                       int32_t *__restrict__ status, int B, int T, int L) {
-    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    // one warp per sentence, lanes over the (step, sub-strip) pairs
+    const int b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (b >= B) return;
     const long long ol = output_length[b], tl = target_length[b];
     if (!lengths_valid(ol, tl, T, L)) {
-        flag[b] = 0;  // nothing to recompute: the loss is -inf by definition
+        if (lane == 0) flag[b] = 0;  // nothing to recompute: the loss is -inf by definition
         return;
     }
-    if (flag[b] != 0) {  // set by the prep or the sweep kernel: an input below 2^-100
-        if (status) atomicOr(status, DAT_STATUS_FAST_FALLBACK);
+    const int bits = flag[b];
+    __syncwarp();
+    if (bits & kFlagTiny) {  // set by the prep or a sweep kernel: an input below 2^kMinLog2Input
+        if (lane == 0) {
+            flag[b] = kFlagRedo;
+            if (status) atomicOr(status, DAT_STATUS_FAST_FALLBACK);
+        }
         return;
     }
     const double *offs = offsets_all + (size_t)b * (2 * T + 2);
@@ -442,12 +479,39 @@ __global__ void dag_fast_check_kernel(const double *__restrict__ offsets_all, co
     const double z2a = offs[2 * T], z2b = offs[2 * T + 1];
     bool bad = !(z2a > -INFINITY && z2a < INFINITY && z2b > -INFINITY && z2b < INFINITY);
     if (!bad) bad = !(fabs(z2a - z2b) <= 1e-3 * (1.0 + fabs(z2b)));
-    for (int t = 0; t + 1 < (int)tl && !bad; t++) {
-        const float r = chk_a[t] + chk_bb[t] - (float)z2b;
-        bad = !(r <= kMaxSpread);
+    const float z2 = (float)z2b;
+    float r_row = -INFINITY;
+    for (int t = lane; t + 1 < (int)tl; t += 32) {
+        const float r = chk_a[t] + chk_bb[t] - z2;
+        if (!(r <= 1e30f)) bad = true;   // NaN / inf
+        r_row = fmaxf(r_row, r);
     }
-    flag[b] = bad ? 1 : 0;
-    if (bad && status) atomicOr(status, DAT_STATUS_FAST_FALLBACK);
+    r_row = warp_max(r_row);
+    const bool local = sub_all != nullptr && !(bits & kFlagHole);   // the sub-strip bound applies
+    if (!local) bad |= !(r_row <= kMaxSpread);
+    if (local) {
+        const float *sa = sub_all + (size_t)b * 2 * T * nH, *sb = sa + (size_t)T * nH;
+        const int nsub = ((int)ol + 31) >> 5;
+        const int pairs = ((int)tl - 1) * nsub;
+        for (int x = lane; x < pairs; x += 32) {
+            const int t = x / nsub, h = x - t * nsub;
+            const float a = sa[t * nH + h];
+            if (!(a > -INFINITY)) continue;
+            // vertices 32h .. 32h+31 are the reversed sweep's canonical vertices ol-1-32h-31 .. ol-1-32h
+            int ulo = (int)ol - 32 - 32 * h, uhi = (int)ol - 1 - 32 * h;
+            ulo = ulo > 0 ? ulo : 0;
+            const float bb = fmaxf(sb[t * nH + (ulo >> 5)], sb[t * nH + (uhi >> 5)]);
+            if (!(a + bb - z2 <= kMaxSpreadLocal)) bad = true;
+        }
+    }
+    bad = __any_sync(0xffffffffu, bad);
+    if (lane == 0) {
+        int verdict = 0;
+        if (bad) verdict = kFlagRedo;
+        else if (!(r_row <= kMaxSpreadBackward)) verdict = kFlagExactBackward;
+        flag[b] = verdict;
+        if (verdict == kFlagRedo && status) atomicOr(status, DAT_STATUS_FAST_FALLBACK);
+    }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -570,19 +634,27 @@ dag_fast_grad_links_kernel(const float *__restrict__ grad_out, const float *__re
     }
 }
 
-// number of sentences the forward handed to the exact kernels
+// count[0]: sentences the forward handed to the exact kernels; count[1]: sentences whose forward was
+// kept but whose grad_links goes to the exact kernel
 __global__ void dag_fast_flagged_kernel(const int *__restrict__ flag, int32_t *__restrict__ count, int B) {
-    int n = 0;
-    for (int b = threadIdx.x; b < B; b += blockDim.x) n += flag[b] != 0;
+    int n = 0, m = 0;
+    for (int b = threadIdx.x; b < B; b += blockDim.x) {
+        n += flag[b] == kFlagRedo;
+        m += flag[b] == kFlagExactBackward;
+    }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
-    __shared__ int part[32];
-    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = n;
+    for (int o = 16; o > 0; o >>= 1) {
+        n += __shfl_xor_sync(0xffffffffu, n, o);
+        m += __shfl_xor_sync(0xffffffffu, m, o);
+    }
+    __shared__ int part[2][32];
+    if ((threadIdx.x & 31) == 0) { part[0][threadIdx.x >> 5] = n; part[1][threadIdx.x >> 5] = m; }
     __syncthreads();
     if (threadIdx.x == 0) {
-        int t = 0;
-        for (int w = 0; w < (int)(blockDim.x >> 5); w++) t += part[w];
-        *count = t;
+        int t = 0, u = 0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); w++) { t += part[0][w]; u += part[1][w]; }
+        count[0] = t;
+        count[1] = u;
     }
 }
 
@@ -605,7 +677,7 @@ int launch_exact_grad_links(const float *grad_output, const float *alpha, const 
 // The strip-ordered sweep keeps every row of a sentence in shared memory; when that fits it is the
 // forward path, and the square exp(links) copy is only built by the backward pass that reads it.
 // + 4: the tensor-core operand loads of 8 consecutive rows then hit distinct banks
-static inline int strip_row_pitch(int prelen) { return ((prelen + 63) & ~63) + 4; }
+static inline int strip_row_pitch(int prelen) { return strip_row_pitch_hd(prelen); }
 static inline bool strip_applicable(int tarlen, int prelen, const DeviceInfo &di) {
     return strip_smem_floats(tarlen, strip_row_pitch(prelen)) * sizeof(float) + 512 <= (size_t)di.max_smem_optin;
 }
@@ -710,8 +782,8 @@ int dat_dag_loss_fast(const float *match_all, const float *links, const int64_t 
                                  (int)strip_smem) != cudaSuccess)
             return check_launch("dat_dag_loss_fast(attr)");
         dag_strip_sweep_kernel<<<2u * (unsigned)bsz, kStripThreads, strip_smem, st>>>(
-            match_all, links, output_length, target_length, order, alpha, beta, offsets, sc.chk, sc.flag,
-            loss, status, tarlen, prelen, translen, strip_rp);
+            match_all, links, output_length, target_length, order, alpha, beta, offsets, sc.chk, sc.sub,
+            sc.flag, loss, status, tarlen, prelen, translen, strip_rp);
         if (int rc = check_launch("dat_dag_loss_fast(strip sweep)")) return rc;
     } else {
         {
@@ -732,8 +804,9 @@ int dat_dag_loss_fast(const float *match_all, const float *links, const int64_t 
             loss, status, tarlen, prelen, translen, rows, pitch);
         if (int rc = check_launch("dat_dag_loss_fast(sweep)")) return rc;
     }
-    dag_fast_check_kernel<<<(bsz + 127) / 128, 128, 0, st>>>(offsets, sc.chk, output_length, target_length,
-                                                            sc.flag, status, bsz, tarlen, prelen);
+    dag_fast_check_kernel<<<(bsz + 3) / 4, 128, 0, st>>>(
+        offsets, sc.chk, strip_applicable(tarlen, prelen, di) ? sc.sub : nullptr, fast_sub_strips(prelen),
+        output_length, target_length, sc.flag, status, bsz, tarlen, prelen);
     if (int rc = check_launch("dat_dag_loss_fast(check)")) return rc;
     // flagged sentences only; all other CTAs return at once
     return launch_exact_sweeps(match_all, links, output_length, target_length, sc.flag, alpha, beta,

@@ -26,7 +26,7 @@
 // At the end the rows are written out exactly like the other paths write them: log2 values
 // relative to one fp64 offset per row, plus the row maxima dag_fast_check_kernel needs.
 // Anything that underflows is 2^-126 below the unit it is added in, which sits within 2^64 of the
-// largest term, i.e. inside what the check's bound covers; inputs below 2^-100 flag the sentence
+// largest term, i.e. inside what the check's bound covers; inputs below 2^-120 flag the sentence
 // as in the tiled kernel.
 #pragma once
 
@@ -75,12 +75,28 @@ __device__ __forceinline__ void strip_load_raw(float (&l)[32], const float *__re
         }
     }
 }
-// in place: e[r] = exp(l[r]); `tiny` collects finite inputs below 2^kMinLog2Input
-__device__ __forceinline__ void strip_exp_block(float (&e)[32], bool &tiny) {
+// What the sweep remembers about the size of its inputs (log2 units), one pair per thread:
+//   fin: the smallest FINITE link or in-window match it used (below kMinLog2Input: "tiny");
+//   all: the smallest link between two vertices of the graph that the band reaches (-inf: a "hole").
+// Both are looked at where the values are consumed, so that the loads stay in flight until then.
+struct StripInputRange {
+    float fin, all;
+};
+__device__ __forceinline__ void strip_note_finite(StripInputRange &ir, float l2) {
+    ir.fin = fminf(ir.fin, l2 > -INFINITY ? l2 : INFINITY);
+}
+// in place: e[r] = exp(l[r]) for the block strip_load_raw fetched (same c, h)
+__device__ __forceinline__ void strip_exp_block(float (&e)[32], int c, int h, int lane, int K, int ol,
+                                                StripInputRange &ir) {
+    const int u = 32 * h + lane;
+    const int d0 = u - 32 * c - 1;
+    const bool full = h > c && 32 * (h - c) + 30 < K && 32 * h + 31 < ol;   // warp-uniform, as in strip_load_raw
 #pragma unroll
     for (int r = 0; r < 32; r++) {
         const float l2 = e[r] * kLog2e;
-        tiny |= (l2 < kMinLog2Input) && (l2 > -INFINITY);
+        strip_note_finite(ir, l2);
+        const int d = d0 - r;
+        ir.all = fminf(ir.all, (full || (d >= 0 && d < K && u < ol)) ? l2 : INFINITY);
         e[r] = ex2(l2);
     }
 }
@@ -156,7 +172,7 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const unsigned (&a)[4], 
 // B rows t4, t4+4, column g8; C rows g8, g8+8, columns 2 t4, 2 t4 + 1.
 __device__ __forceinline__ void strip_bulk_mma(const float *__restrict__ links, const StripSmem &sm, int h0,
                                                int gs, int t0, int t1, int tid, int K, int ol, int rp,
-                                               int nH, bool rev, bool &tiny) {
+                                               int nH, bool rev, StripInputRange &ir) {
     const int lane = tid & 31, warp = tid >> 5;
     const int k = warp & 3, mt = warp >> 2, g8 = lane >> 2, t4 = lane & 3;
     int cmin = h0 - (K - 1) / 32 - 1;   // blocks further back hold no link into the group
@@ -194,24 +210,35 @@ __device__ __forceinline__ void strip_bulk_mma(const float *__restrict__ links, 
                 int r, col;
                 tile_rc(q, r, col);
                 const float l2 = nxt[q] * kLog2e;
-                tiny |= (l2 < kMinLog2Input) && (l2 > -INFINITY);
+                strip_note_finite(ir, l2);
+                const int u = 32 * h0 + col;
+                ir.all = fminf(ir.all, ((u - 32 * c - r - 1 < K) && u < ol) ? l2 : INFINITY);
                 sm.Et[r * kEtPitch + col] = ex2(l2);
             }
             __syncthreads();
             if (c + 1 < h0) tile_load(c + 1, nxt);
-            // scale of the two A rows this lane holds: steps s0 + g8 and s0 + g8 + 8
-            float asc[2];
+            // scale of the two A rows this lane holds (steps s0 + g8 and s0 + g8 + 8): 2^(sc - g), applied
+            // as two exact power-of-two factors so that an entry only vanishes when it is really below
+            // 2^-126 in the step's unit, i.e. 2^-190 below the largest entry of the finished groups
+            // (the second factor is 1 in the usual case)
+            float as1[2], as2[2];
 #pragma unroll
             for (int q = 0; q < 2; q++) {
                 const int sx = s0 + g8 + 8 * q;
-                float f = 0.f;
+                float f1 = 0.f, f2 = 0.f;
                 if (k < gs && sx <= t1) {
                     const int e = sm.sc[(sx - 1) * nH + c];
-                    if (e != kExpNone) f = pow2_flush(e - sm.g[sx - 1]);
+                    int kx = e - sm.g[sx - 1];   // <= 0
+                    if (e != kExpNone && kx >= -252) {
+                        const int k1 = kx >= -126 ? kx : kx / 2;
+                        f1 = __int_as_float((k1 + 127) << 23);
+                        f2 = __int_as_float((kx - k1 + 127) << 23);
+                    }
                 }
-                asc[q] = f;
+                as1[q] = f1;
+                as2[q] = f2;
             }
-            if (__any_sync(0xffffffffu, asc[0] != 0.f || asc[1] != 0.f)) {
+            if (__any_sync(0xffffffffu, as1[0] != 0.f || as1[1] != 0.f)) {
 #pragma unroll
                 for (int kk = 0; kk < 4; kk++) {
                     unsigned ahi[4], alo[4];
@@ -219,8 +246,8 @@ __device__ __forceinline__ void strip_bulk_mma(const float *__restrict__ links, 
                     for (int q = 0; q < 4; q++) {   // (row g8 + 8 (q & 1), source t4 + 4 (q >> 1))
                         const int sx = s0 + g8 + 8 * (q & 1);
                         float a = 0.f;
-                        if (asc[q & 1] != 0.f)
-                            a = sm.Y[(size_t)(sx - 1) * rp + 32 * c + 8 * kk + t4 + 4 * (q >> 1)] * asc[q & 1];
+                        if (as1[q & 1] != 0.f)
+                            a = (sm.Y[(size_t)(sx - 1) * rp + 32 * c + 8 * kk + t4 + 4 * (q >> 1)] * as1[q & 1]) * as2[q & 1];
                         ahi[q] = to_tf32(a);
                         alo[q] = to_tf32(a - __uint_as_float(ahi[q]));
                     }
@@ -270,7 +297,7 @@ struct StripCarry {
 // below the largest term.
 __device__ __forceinline__ void strip_diag_step(const StripSmem &sm, const float (&ed)[32], int h, int k, int s,
                                                 int lane, int ol, int W, int rp, int nH, bool want_v,
-                                                StripCarry &cy, bool &tiny) {
+                                                StripCarry &cy, StripInputRange &ir) {
     const int u = 32 * h + lane, pc = 32 * k + lane, ring = (k * kRing + (s & (kRing - 1)));
     // ---- independent of the previous step's result
     const int U = sm.g[s - 1];
@@ -283,7 +310,7 @@ __device__ __forceinline__ void strip_diag_step(const StripSmem &sm, const float
     if (lane == 0) sm.Pe[ring] = kExpNone;
     const float m2 = sm.M[(s & (kMRing - 1)) * kGroupCols + pc] * kLog2e;
     const bool inside = u >= s && u <= s + W - 1 && u < ol;
-    tiny |= (m2 < kMinLog2Input) && (m2 > -INFINITY) && inside;
+    ir.fin = fminf(ir.fin, (inside && m2 > -INFINITY) ? m2 : INFINITY);
     const float pm = inside ? ex2(m2) : 0.f;
     // values are >= 0 (or inf/NaN from bad inputs, which order above every finite float as bits)
     const unsigned fbits = __reduce_max_sync(0xffffffffu, __float_as_uint(far));
@@ -350,8 +377,8 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
                        const int64_t *__restrict__ output_length, const int64_t *__restrict__ target_length,
                        const int *__restrict__ order, float *__restrict__ alpha_all,
                        float *__restrict__ beta_all, double *__restrict__ offsets_all,
-                       float *__restrict__ chk_all, int *__restrict__ flag, float *__restrict__ loss,
-                       int32_t *__restrict__ status, int T, int L, int K, int rp) {
+                       float *__restrict__ chk_all, float *__restrict__ sub_all, int *__restrict__ flag,
+                       float *__restrict__ loss, int32_t *__restrict__ status, int T, int L, int K, int rp) {
     extern __shared__ __align__(16) float ssm[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool rev = blockIdx.x & 1;   // odd CTAs: the beta recursion (reversed graph)
@@ -396,11 +423,13 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
     }
     for (int x = tid; x < T; x += kStripThreads) sm.g[x] = kExpNone;
     __syncthreads();
-    bool tiny = false;
+    StripInputRange ir;
+    ir.fin = INFINITY;
+    ir.all = K < ol - 1 ? -INFINITY : INFINITY;   // a band narrower than the graph: vertex pairs without a link
     if (tid == 0) {
         // step 0: only canonical vertex 0, value exp(match) = 2^m0
         const float m0 = (rev ? match[(size_t)(tl - 1) * L + (ol - 1)] : match[0]) * kLog2e;
-        tiny |= (m0 < kMinLog2Input) && (m0 > -INFINITY);
+        strip_note_finite(ir, m0);
         if (m0 > -INFINITY && m0 < INFINITY) {
             const float fl = floorf(m0);
             sm.Y[0] = ex2(m0 - fl);
@@ -445,8 +474,8 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
         }
         if (kd0 >= 0) strip_load_raw(eb0, links, h0 + ks0, h0 + kd0, lane, K, ol, rev);
         // ---- phase 1: everything the finished groups send into this group
-        if (h0 > 0) strip_bulk_mma(links, sm, h0, gs, t0, t1, tid, K, ol, rp, nH, rev, tiny);
-        if (kd0 >= 0) strip_exp_block(eb0, tiny);
+        if (h0 > 0) strip_bulk_mma(links, sm, h0, gs, t0, t1, tid, K, ol, rp, nH, rev, ir);
+        if (kd0 >= 0) strip_exp_block(eb0, h0 + ks0, h0 + kd0, lane, K, ol, ir);
         strip_cp_async_wait_all();
         __syncthreads();
         // ---- phase 2: pipelined walk.  In iteration tau the diagonal block of sub-strip k does step
@@ -467,7 +496,7 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
             if (kd0 >= 0) {
                 const int s = tau - ks0;
                 if (s >= t0 && s <= t1) {
-                    if (ks0 == kd0) strip_diag_step(sm, eb0, h0 + kd0, kd0, s, lane, ol, W, rp, nH, rev, cy, tiny);
+                    if (ks0 == kd0) strip_diag_step(sm, eb0, h0 + kd0, kd0, s, lane, ol, W, rp, nH, rev, cy, ir);
                     else strip_cross_step(sm, eb0, h0, ks0, kd0, s, lane, rp, nH);
                 }
             }
@@ -490,16 +519,22 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
         }
         __syncthreads();
     }
-    if (tiny) flag[b] = 1;   // benign race: every writer stores the same value
+    if (ir.fin < kMinLog2Input) atomicOr(flag + b, kFlagTiny);
+    if (ir.all == -INFINITY) atomicOr(flag + b, kFlagHole);
 
     // ---- write the rows out: log2 values relative to one fp64 offset per row
+    float *sub = sub_all + ((size_t)b * 2 + (rev ? 1 : 0)) * T * nH;   // log2 maxima per (step, sub-strip)
     for (int s = warp; s < tl; s += kStripWarps) {
         float ry = -INFINITY, rv = -INFINITY;
         for (int h = lane; h < nH; h += 32) {
             const unsigned yb = sm.mxy[s * nH + h], vb = sm.mxv[s * nH + h];
             const float e = (float)sm.sc[s * nH + h];
-            if (yb != 0u) ry = fmaxf(ry, lg2(__uint_as_float(yb)) + e);
-            if (vb != 0u) rv = fmaxf(rv, lg2(__uint_as_float(vb)) + e);
+            float hy = -INFINITY, hv = -INFINITY;
+            if (yb != 0u) hy = lg2(__uint_as_float(yb)) + e;
+            if (vb != 0u) hv = lg2(__uint_as_float(vb)) + e;
+            ry = fmaxf(ry, hy);
+            rv = fmaxf(rv, hv);
+            sub[(rev ? tl - 1 - s : s) * nH + h] = rev ? hv : hy;   // canonical sub-strip index
         }
         ry = warp_max(ry);
         rv = warp_max(rv);

@@ -332,7 +332,7 @@ dag_sweep_kernel(const float *__restrict__ match, const float *__restrict__ link
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int b = blockIdx.x / nsweep;
     const int sweep = blockIdx.x - b * nsweep;
-    if (select != nullptr && select[b] == 0) return;  // sentence already done by the fast path
+    if (select != nullptr && select[b] != 1) return;  // only the sentences the fast path gave up on (verdict 1)
     const long long ol = output_length[b], tl = target_length[b];
     double *offs = offsets + (size_t)b * (2 * T + 2);
     if (!lengths_valid(ol, tl, T, L)) {

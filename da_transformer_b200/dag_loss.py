@@ -100,9 +100,11 @@ class DagLossFunc(Function):
     config = 1
     config1 = 2
     config2 = 2
-    # False: when gradients are needed the forward runs the fast probability-domain kernels,
-    # which fall back per sentence to the exact log-domain kernels whenever their dynamic-range
-    # check does not pass.  True: always the exact log-domain kernels.
+    # False: the forward runs the fast probability-domain kernels, which fall back per sentence to
+    # the exact log-domain kernels whenever their dynamic-range check does not pass.  Calls without
+    # gradient (validation) take them too: the check needs both recursions, and both fast sweeps
+    # together are still several times faster than the exact alpha recursion alone.
+    # True: always the exact log-domain kernels.
     exact = False
 
     @staticmethod
@@ -121,12 +123,14 @@ class DagLossFunc(Function):
         dev = match_all.device
         L = lib()
         with torch.cuda.device(dev):
+            fast = not DagLossFunc.exact and bsz > 0
             alpha = torch.empty(bsz, tarlen, prelen, dtype=torch.float32, device=dev)
-            beta = torch.empty(bsz, tarlen, prelen, dtype=torch.float32, device=dev) if require_gradient else None
+            beta = (torch.empty(bsz, tarlen, prelen, dtype=torch.float32, device=dev)
+                    if (require_gradient or fast) else None)
             offsets = torch.empty(bsz, 2 * tarlen + 2, dtype=torch.float64, device=dev)
             res = torch.empty(bsz, dtype=torch.float32, device=dev)
             scratch = None
-            if require_gradient and not DagLossFunc.exact and bsz > 0:
+            if fast:
                 scratch = torch.empty(L.dat_dag_loss_fast_scratch_bytes(bsz, tarlen, prelen),
                                       dtype=torch.uint8, device=dev)
                 check(L.dat_dag_loss_fast(ptr(match_all), ptr(links), ptr(output_length),

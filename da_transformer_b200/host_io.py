@@ -1,0 +1,40 @@
+"""Feeding the ops from host memory.
+
+DA-Transformer produces ``links`` on the device, so the reference never moves them over PCIe; a
+caller that does keep them in host memory (a data-loading or serving process in front of the ops)
+should not pay for the half of the band that is padding.  ``upload_links`` moves only the entries a
+graph can have (``dat_upload_links``); everything else of the device tensor is left untouched, which
+is safe because no op of this package reads a link whose destination is not below ``output_length``.
+"""
+import torch
+
+from ._native import check, lib, ptr, stream_ptr
+
+__all__ = ["upload_links", "upload_links_bytes"]
+
+
+def upload_links_bytes(bsz, prelen, translen, max_output_length):
+    """Bytes ``upload_links`` moves for these sizes."""
+    return int(lib().dat_upload_links_bytes(int(bsz), int(prelen), int(translen), int(max_output_length)))
+
+
+def upload_links(host_links, out, max_output_length=None):
+    """Copies the real entries of the band ``host_links`` [B,L,K] (fp32, contiguous, ideally pinned)
+    into the CUDA tensor ``out`` of the same shape, on the current stream, without blocking when the
+    source is pinned.  ``max_output_length``: the largest ``output_length`` of the batch (default L).
+    The padding of ``out`` keeps whatever it held; initialise it once (e.g. with -inf) if anything
+    other than this package's ops will read it."""
+    if host_links.is_cuda or not out.is_cuda:
+        raise RuntimeError("upload_links copies from a host tensor to a CUDA tensor")
+    if host_links.shape != out.shape or host_links.dim() != 3:
+        raise RuntimeError("host_links and out must be [batch, prelen, translen] tensors of the same shape")
+    if host_links.dtype != torch.float32 or out.dtype != torch.float32:
+        raise RuntimeError("links are float32")
+    if not host_links.is_contiguous() or not out.is_contiguous():
+        raise RuntimeError("host_links and out must be contiguous")
+    bsz, prelen, translen = host_links.shape
+    n = prelen if max_output_length is None else int(max_output_length)
+    with torch.cuda.device(out.device):
+        check(lib().dat_upload_links(ptr(host_links), ptr(out), bsz, prelen, translen, n, stream_ptr(out.device)),
+              "upload_links")
+    return out

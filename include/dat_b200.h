@@ -165,9 +165,10 @@ int dat_dag_loss_fast(const float *match_all, const float *links, const int64_t 
                       float *loss, int32_t *status, void *scratch,
                       int bsz, int tarlen, int prelen, int translen, void *stream);
 
-/* Number of sentences of the last dat_dag_loss_fast call on `scratch` that its dynamic-range check
- * handed to the exact kernels, written to the device word *count (no counterpart in the reference;
- * it is what the status bit DAT_STATUS_FAST_FALLBACK summarises). */
+/* What the dynamic-range check of the last dat_dag_loss_fast call on `scratch` decided, as two device
+ * words: count[0] = sentences recomputed by the exact kernels (what the status bit
+ * DAT_STATUS_FAST_FALLBACK summarises), count[1] = sentences whose forward was kept but whose
+ * grad_links will come from the exact kernel.  No counterpart in the reference. */
 int dat_dag_loss_fast_flagged(const void *scratch, int32_t *count, int bsz, int tarlen, int prelen,
                               void *stream);
 
@@ -314,6 +315,19 @@ int dat_viterbi_decode(const float *links_square, const float *unreduced_logits,
                        int64_t *out_tokens, int64_t *out_length, int64_t *out_vertices, float *out_score,
                        int32_t *status, int bsz, int prelen, int max_length, int joint, float beta,
                        int64_t pad_index, void *stream);
+
+/*
+ * Host-to-device copy of band links [bsz,prelen,translen] that skips the padding (no counterpart in the
+ * reference, whose callers keep the links on the device): row i of a graph with n vertices has n-1-i
+ * real entries, the rest is -inf that no entry point of this library reads.  Copies, for all
+ * sentences at once, the staircase of 32-row blocks that covers the entries a graph of
+ * max_output_length vertices can have; the other bytes of dev_links are left as they are.
+ * host_links should be page-locked for the copies to be asynchronous.  Enqueued on `stream`.
+ * dat_upload_links_bytes: the number of bytes that call moves (for accounting).
+ */
+size_t dat_upload_links_bytes(int bsz, int prelen, int translen, int max_output_length);
+int dat_upload_links(const float *host_links, float *dev_links, int bsz, int prelen, int translen,
+                     int max_output_length, void *stream);
 
 #ifdef __cplusplus
 }

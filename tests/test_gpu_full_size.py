@@ -11,7 +11,7 @@ import torch
 from oracle import oracle, ref_cuda
 from da_transformer_b200 import (DagLossFunc, dag_best_alignment, dag_logsoftmax_gather_inplace, dag_loss,
                                  last_status, workloads)
-from util import assert_rel, assert_rel_per_sentence, assert_rel_quantized, rel_err
+from util import assert_rel, assert_rel_per_sentence, assert_rel_quantized, plain_tol_16bit, rel_err
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -54,7 +54,7 @@ def test_gather_on_the_full_c2_tensor(dtype):
         assert_rel(sel[b, l].detach().cpu().numpy()[None, None], ref_sel, TOL_SEL, f"sel row {(b, l)}")
         got = dx[b, l].float().cpu().numpy()[None, None]
         assert_rel_quantized(got, ref_dx, TOL_GRAD_HALF, name16, f"dlogits row {(b, l)}")
-        assert_rel(got, ref_dx, TOL_GRAD_HALF, f"dlogits row {(b, l)}, plain rule")
+        assert_rel(got, ref_dx, plain_tol_16bit(name16, TOL_GRAD_HALF), f"dlogits row {(b, l)}, plain rule")
     # a log-softmax gradient sums to zero over the vocabulary, on every row of the tensor
     rs = torch.zeros(B, L, device=DEV)
     for b in range(B):
