@@ -334,6 +334,10 @@ def main():
     ap.add_argument("--no-gather", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the C1 / C3 / peaky-workload legs")
     ap.add_argument("--eager", action="store_true", help="launch the step kernel by kernel instead of replaying a CUDA graph")
+    ap.add_argument("--gather-only", action="store_true",
+                    help="only the logsoftmax_gather leg (bf16, V=32000) on --gather-batch sentences: the small case "
+                         "the profiler captures")
+    ap.add_argument("--gather-batch", type=int, default=32)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     args.repeats = max(args.repeats, 1)
@@ -365,6 +369,31 @@ def main():
         fn.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
     peaks, peak_kind = measured_peaks()
     ptr, sptr = _native.ptr, _native.stream_ptr
+
+    if args.gather_only:
+        Bg, Lg, Vg, Sg = args.gather_batch, 1024, 32000, 128
+        g2 = torch.Generator(device=dev)
+        g2.manual_seed(workloads.BASE_SEED + 2)
+        base = (torch.randn(Bg, Lg, Vg, device=dev, generator=g2) * 2.0).to(torch.bfloat16)
+        idx = torch.randint(0, Vg, (Bg, Lg, Sg), device=dev, generator=g2)
+        gsel = torch.randn(Bg, Lg, Sg, device=dev, generator=g2)
+        times = []
+        for it in range(args.warmup + args.steps):
+            x = base.clone().requires_grad_()
+            work = x.clone()
+            a, b_, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            a.record()
+            _, sel = dag_logsoftmax_gather_inplace(work, idx)
+            b_.record()
+            sel.backward(gsel)
+            c.record()
+            torch.cuda.synchronize()
+            if it >= args.warmup:
+                times.append((a.elapsed_time(b_), b_.elapsed_time(c)))
+        print(json.dumps({"gather_only": {"shape": [Bg, Lg, Vg], "dtype": "bfloat16",
+                                          "fwd_ms": statistics.median(t[0] for t in times),
+                                          "bwd_ms": statistics.median(t[1] for t in times)}}))
+        return
 
     # ---- data: every rank owns one shard of 512 sentences
     # (shard r is drawn from its own generator, seed 20225 + 1000 r, so it is the same data whatever
@@ -788,8 +817,8 @@ def main():
 
 
 # dram bytes (read + write) of one forward + one backward launch of the gather on C2 bf16 V=32000
-# (profiles/lsg_c2_bf16_v32000.md); None until that capture exists for the current kernels
-GATHER_TRAFFIC_BYTES = None
+# (profiles/lsg_c2_bf16_v32000.md: measured on [8,1024,32000], traffic proportional to rows)
+GATHER_TRAFFIC_BYTES = 4 * (532.80e6 + 4.44e6 + 536.98e6 + 467.87e6)   # captured on 8 of the 32 sentences
 
 
 def extra_legs(torch, dev, ev, workloads, dag_loss, dag_best_alignment, dag_logsoftmax_gather_inplace, DagLossFunc,

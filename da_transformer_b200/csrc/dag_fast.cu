@@ -437,7 +437,7 @@ dag_fast_sweep_kernel(const float *__restrict__ match_all, const float *__restri
     }
 }
 
-// One warp per sentence: the verdict on what the probability-domain sweeps left behind.
+// One small CTA per sentence: the verdict on what the probability-domain sweeps left behind.
 // What they can lose is what underflowed in the unit it was added in.  Two bounds cover it:
 //  * everything is within 2^-190 of the largest entry of its own 32-vertex sub-strip at that step
 //    (rows, in-group sums), so with R_sub = max over (t, sub-strip) of
@@ -452,23 +452,25 @@ dag_fast_sweep_kernel(const float *__restrict__ match_all, const float *__restri
 //    stay below kMaxSpread instead (the tiled sweep, whose rows have a single unit, always needs that).
 // The product form of grad_links multiplies factors of size 2^(R_t / 2); beyond kMaxSpreadBackward its
 // factors would underflow where they matter, so those sentences get the exact grad_links kernel.
-__global__ void dag_fast_check_kernel(const double *__restrict__ offsets_all, const float *__restrict__ chk_all,
+constexpr int kCheckThreads = 128;
+__global__ void __launch_bounds__(kCheckThreads)
+dag_fast_check_kernel(const double *__restrict__ offsets_all, const float *__restrict__ chk_all,
                                       const float *__restrict__ sub_all, int nH,
                                       const int64_t *__restrict__ output_length,
                                       const int64_t *__restrict__ target_length, int *__restrict__ flag,
                                       int32_t *__restrict__ status, int B, int T, int L) {
-    // one warp per sentence, lanes over the (step, sub-strip) pairs
-    const int b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (b >= B) return;
+    // one CTA of kCheckThreads per sentence, threads over the (step, sub-strip) pairs
+    const int b = blockIdx.x, tid = threadIdx.x;
+    __shared__ float row_s[kCheckThreads / 32];
     const long long ol = output_length[b], tl = target_length[b];
     if (!lengths_valid(ol, tl, T, L)) {
-        if (lane == 0) flag[b] = 0;  // nothing to recompute: the loss is -inf by definition
+        if (tid == 0) flag[b] = 0;  // nothing to recompute: the loss is -inf by definition
         return;
     }
     const int bits = flag[b];
-    __syncwarp();
+    __syncthreads();
     if (bits & kFlagTiny) {  // set by the prep or a sweep kernel: an input below 2^kMinLog2Input
-        if (lane == 0) {
+        if (tid == 0) {
             flag[b] = kFlagRedo;
             if (status) atomicOr(status, DAT_STATUS_FAST_FALLBACK);
         }
@@ -481,19 +483,19 @@ __global__ void dag_fast_check_kernel(const double *__restrict__ offsets_all, co
     if (!bad) bad = !(fabs(z2a - z2b) <= 1e-3 * (1.0 + fabs(z2b)));
     const float z2 = (float)z2b;
     float r_row = -INFINITY;
-    for (int t = lane; t + 1 < (int)tl; t += 32) {
+    for (int t = tid; t + 1 < (int)tl; t += kCheckThreads) {
         const float r = chk_a[t] + chk_bb[t] - z2;
         if (!(r <= 1e30f)) bad = true;   // NaN / inf
         r_row = fmaxf(r_row, r);
     }
     r_row = warp_max(r_row);
+    if ((tid & 31) == 0) row_s[tid >> 5] = r_row;
     const bool local = sub_all != nullptr && !(bits & kFlagHole);   // the sub-strip bound applies
-    if (!local) bad |= !(r_row <= kMaxSpread);
     if (local) {
         const float *sa = sub_all + (size_t)b * 2 * T * nH, *sb = sa + (size_t)T * nH;
         const int nsub = ((int)ol + 31) >> 5;
         const int pairs = ((int)tl - 1) * nsub;
-        for (int x = lane; x < pairs; x += 32) {
+        for (int x = tid; x < pairs; x += kCheckThreads) {
             const int t = x / nsub, h = x - t * nsub;
             const float a = sa[t * nH + h];
             if (!(a > -INFINITY)) continue;
@@ -504,8 +506,11 @@ __global__ void dag_fast_check_kernel(const double *__restrict__ offsets_all, co
             if (!(a + bb - z2 <= kMaxSpreadLocal)) bad = true;
         }
     }
-    bad = __any_sync(0xffffffffu, bad);
-    if (lane == 0) {
+    bad = __syncthreads_or(bad);
+    if (tid == 0) {
+        r_row = row_s[0];
+        for (int w = 1; w < kCheckThreads / 32; w++) r_row = fmaxf(r_row, row_s[w]);
+        if (!local) bad |= !(r_row <= kMaxSpread);
         int verdict = 0;
         if (bad) verdict = kFlagRedo;
         else if (!(r_row <= kMaxSpreadBackward)) verdict = kFlagExactBackward;
@@ -679,7 +684,10 @@ int launch_exact_grad_links(const float *grad_output, const float *alpha, const 
 // + 4: the tensor-core operand loads of 8 consecutive rows then hit distinct banks
 static inline int strip_row_pitch(int prelen) { return strip_row_pitch_hd(prelen); }
 static inline bool strip_applicable(int tarlen, int prelen, const DeviceInfo &di) {
-    return strip_smem_floats(tarlen, strip_row_pitch(prelen)) * sizeof(float) + 512 <= (size_t)di.max_smem_optin;
+    // all rows in shared memory, and the [128 x steps] accumulator of the tensor-core phase within the 512
+    // columns of tensor memory
+    return strip_step_pad(tarlen) <= 512 &&
+           strip_smem_floats(tarlen, strip_row_pitch(prelen)) * sizeof(float) + 512 <= (size_t)di.max_smem_optin;
 }
 
 }  // namespace dat
@@ -804,7 +812,7 @@ int dat_dag_loss_fast(const float *match_all, const float *links, const int64_t 
             loss, status, tarlen, prelen, translen, rows, pitch);
         if (int rc = check_launch("dat_dag_loss_fast(sweep)")) return rc;
     }
-    dag_fast_check_kernel<<<(bsz + 3) / 4, 128, 0, st>>>(
+    dag_fast_check_kernel<<<(unsigned)bsz, kCheckThreads, 0, st>>>(
         offsets, sc.chk, strip_applicable(tarlen, prelen, di) ? sc.sub : nullptr, fast_sub_strips(prelen),
         output_length, target_length, sc.flag, status, bsz, tarlen, prelen);
     if (int rc = check_launch("dat_dag_loss_fast(check)")) return rc;

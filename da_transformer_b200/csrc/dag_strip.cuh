@@ -10,10 +10,11 @@
 // One CTA per (sentence, direction).  In canonical coordinates (u, s) the row of step s is
 // y[s][u] * 2^sc[s][u/32]: fp32 mantissas with one power-of-two exponent per 32-vertex sub-strip,
 // all rows resident in shared memory.  Vertices are taken in groups of four sub-strips (128):
-//   phase 1 (16 warps, tensor cores): what the finished groups send into this group.  For each
+//   phase 1 (tensor cores, tcgen05): what the finished groups send into this group.  For each
 //     finished 32-vertex source block c this is, over all steps at once, the product
-//     [steps x 32] x [32 x 128] of the rows y[s-1][32c..32c+31] (scaled to the step's common unit
-//     2^g[s-1]) with the tile of E; see strip_bulk_mma.  No dependency between source blocks.
+//     [128 x 32] x [32 x steps] of the tile of E (transposed: destinations are the rows) with the rows
+//     y[s-1][32c..32c+31] (scaled to the step's common unit 2^g[s-1]); the [128 x steps] sum lives in
+//     tensor memory and the diagonal blocks read their column of it step by step; see strip_bulk_umma.
 //   phase 2 (10 warps, one CTA barrier per iteration): the ten blocks inside the group, one per
 //     warp, walked as a pipeline.  In iteration tau the triangular block of sub-strip k does step
 //     tau - k, and the square block from sub-strip ks to kd does step tau - ks: its sources were
@@ -29,6 +30,8 @@
 // largest term, i.e. inside what the check's bound covers; inputs below 2^-120 flag the sentence
 // as in the tiled kernel.
 #pragma once
+
+#include "umma.cuh"
 
 namespace dat {
 
@@ -117,25 +120,28 @@ constexpr int kGroupSubs = 4;                  // 32-vertex sub-strips per group
 constexpr int kGroupCols = 32 * kGroupSubs;    // 128
 constexpr int kRing = 8;                       // steps an in-group accumulator can be alive (> kGroupSubs)
 constexpr int kMRing = 32;                     // steps of match values staged ahead
-constexpr int kEtPitch = kGroupCols + 8;       // the tensor-core operand loads of a tile hit 32 distinct banks
+constexpr int kUmmaPolls = 1 << 22;            // bound of a wait for the tensor core (never reached)
+__host__ __device__ inline int strip_step_pad(int T) { return (T + 15) & ~15; }   // N of the tensor-core product
 
 struct StripSmem {
     float *Y;       // [T][rp]            mantissas of the rows, canonical vertices
-    float *Pf;      // [T][kGroupCols]    what the finished groups send to the current group, unit 2^g[s-1]
+    float *Ea;      // [2][128 x 32]      tf32 high / low parts of the E tile (destinations x sources), tensor-core layout
+    float *Yb;      // [2][Tpad x 32]     tf32 high / low parts of the scaled rows (steps x sources), same layout
     float *M;       // [kMRing][kGroupCols] match values (natural log) of the current group, ring over steps
     float *Pr;      // [kGroupSubs][kRing][32] what the group's earlier sub-strips send, ring over steps
-    float *Et;      // [32][kEtPitch]     exp(links) from one finished 32-vertex block into the whole group
     int *Pe;        // [kGroupSubs][kRing]     and the exponent of each such accumulator
     int *sc;        // [T][nH]   exponent of each 32-vertex sub-strip (kExpNone: nothing there)
     int *g;         // [T]       largest exponent over the finished groups
     unsigned *mxy;  // [T][nH]   largest entry of a sub-strip, as float bits, in the sub-strip's unit
     unsigned *mxv;  // [T][nH]   the same before the multiplication by exp(match)
+    uint64_t *mbar; // completion barrier of the tensor-core products
+    uint32_t *tmem; // base address of the accumulator in tensor memory
 };
 __host__ __device__ inline size_t strip_smem_floats(int T, int rp) {
     const int nH = rp / 32;
-    return (size_t)T * rp + (size_t)T * kGroupCols + (size_t)kMRing * kGroupCols +
-           (size_t)kGroupSubs * kRing * 32 + 32 * kEtPitch + kGroupSubs * kRing + (size_t)T * nH + T +
-           (size_t)2 * T * nH;
+    return (size_t)T * rp + (size_t)2 * kGroupCols * 32 + (size_t)2 * strip_step_pad(T) * 32 +
+           (size_t)kMRing * kGroupCols + (size_t)kGroupSubs * kRing * 32 + kGroupSubs * kRing + (size_t)T * nH +
+           T + (size_t)2 * T * nH + 8;
 }
 
 // x * 2^k for k in [-252, 254] as two exact power-of-two multiplications; 0 below that range
@@ -148,134 +154,142 @@ __device__ __forceinline__ float scale2(float x, int k) {
     return (x * __int_as_float((k1 + 127) << 23)) * __int_as_float((k2 + 127) << 23);
 }
 
-// The tensor core reads the upper 19 bits of an fp32 operand (sign, exponent, 10 mantissa bits).
-// Splitting by masking costs one logic operation; the rounding conversion instruction runs on
-// the 16-lane special-function unit and was the bottleneck of this phase.
-__device__ __forceinline__ unsigned to_tf32(float x) { return __float_as_uint(x) & 0xffffe000u; }
-__device__ __forceinline__ void mma_tf32(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+// The tensor core reads the upper 19 bits of an fp32 operand (sign, exponent, 10 mantissa bits), so the
+// high part of a split is the value itself with the low mantissa bits masked off; the rounding
+// conversion instruction would run on the 16-lane special-function unit.
+__device__ __forceinline__ float tf32_high(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
+__device__ __forceinline__ void tf32_split4(const float (&v)[4], float4 &hi, float4 &lo) {
+    hi = make_float4(tf32_high(v[0]), tf32_high(v[1]), tf32_high(v[2]), tf32_high(v[3]));
+    lo = make_float4(v[0] - hi.x, v[1] - hi.y, v[2] - hi.z, v[3] - hi.w);
 }
 
-// phase 1: what the finished groups send into the current group, as a matrix product on the
-// tensor cores.  For one 32-vertex source block c and all steps at once
-//     Pf[s][j] += sum_r (y[s-1][32c + r] * 2^(sc[s-1][c] - g[s-1])) * E[32c + r][32 h0 + j],  j < 128,
-// i.e. [steps x 32] x [32 x 128], summed over c.  The CTA loads and exponentiates the
-// [32 x 128] tile of E once per c (the loads of the next tile are in flight while this one is
-// used); warp w owns destination sub-strip w % 4 and the 16 steps t0 + 16 (w / 4) .. (+64 per
-// further pass), keeps its [16 x 32] result in registers over all c and stores it once: no atomics.
-// fp32 accuracy comes from splitting both operands into two tf32 numbers and adding the three
-// leading products (hi*hi + hi*lo + lo*hi) in fp32.
-// Fragment layout of mma.m16n8k8 (g8 = lane / 4, t4 = lane % 4): A rows g8, g8+8, columns t4, t4+4;
-// B rows t4, t4+4, column g8; C rows g8, g8+8, columns 2 t4, 2 t4 + 1.
-__device__ __forceinline__ void strip_bulk_mma(const float *__restrict__ links, const StripSmem &sm, int h0,
-                                               int gs, int t0, int t1, int tid, int K, int ol, int rp,
-                                               int nH, bool rev, StripInputRange &ir) {
+// phase 1: what the finished groups send into the current group, as matrix products on the tensor
+// cores (tcgen05.mma, accumulator in tensor memory).  For one 32-vertex source block c and all steps
+// at once
+//     F[j][s] += sum_r E[32c + r][32 h0 + j] * (y[s-1][32c + r] * 2^(sc[s-1][c] - g[s-1])),  j < 128,
+// i.e. [128 x 32] x [32 x steps], summed over c: D = A * B^T with A = the E tile (row = destination j,
+// K = source r) and B = the scaled rows (row = step s, K = source r), both staged by all threads in
+// the K-major layout of umma.cuh, one thread issuing the instructions.  fp32 accuracy comes from
+// splitting both operands into two tf32 numbers and adding the three leading products
+// (hi*hi + hi*lo + lo*hi) into the same fp32 accumulator.  The [128 lanes x steps] accumulator stays
+// in tensor memory; lane j, column s is what strip_diag_step of sub-strip j / 32 reads at step s.
+// The operand tiles are single-buffered: the products of block c must have finished (mbarrier) before
+// block c + 1 is staged; the links of block c + 1 are in flight meanwhile.
+// Returns false if a wait for the tensor core ran out (the caller then hands the sentence to the
+// exact kernels).
+__device__ __forceinline__ bool strip_bulk_umma(const float *__restrict__ links, const StripSmem &sm, int h0,
+                                                int t0, int t1, int tid, int K, int ol, int rp, int nH,
+                                                int Tpad, bool rev, uint32_t tmem_base, uint32_t &mbar_phase,
+                                                StripInputRange &ir) {
     const int lane = tid & 31, warp = tid >> 5;
-    const int k = warp & 3, mt = warp >> 2, g8 = lane >> 2, t4 = lane & 3;
     int cmin = h0 - (K - 1) / 32 - 1;   // blocks further back hold no link into the group
     cmin = cmin > 0 ? cmin : 0;
-    // tile element q of this thread: forward rows are contiguous along the destination, reversed
-    // ones along the source, so the lanes run along that index
-    const auto tile_rc = [&](int q, int &r, int &col) {
-        if (rev) { r = lane; col = warp + kStripWarps * q; }
-        else { r = (tid >> 7) + 4 * q; col = tid & 127; }
-    };
+    bool ok_all = true;
+    // E tile: a thread owns one destination m and the K chunks kq0, kq0 + 4 (four sources each).  The
+    // lanes of a quarter-warp always hold eight consecutive destinations with the same chunk, so their
+    // 16-byte stores fall into distinct banks; beyond that the lanes run along whatever is contiguous in
+    // memory: the destinations in the forward sweep (a band row holds the links of one source), the
+    // chunks in the reversed sweep (a band row holds the links INTO one canonical destination).
+    const int m = rev ? 8 * warp + (lane & 7) : tid & (kGroupCols - 1);
+    const int kq0 = rev ? lane >> 3 : tid >> 7;
+    const int u = 32 * h0 + m;
     const auto tile_load = [&](int c, float (&v)[8]) {
 #pragma unroll
         for (int q = 0; q < 8; q++) {
-            int r, col;
-            tile_rc(q, r, col);
-            const int up = 32 * c + r, u = 32 * h0 + col, d = u - up - 1;   // d >= 0: c < h0
+            const int r = 4 * (kq0 + 4 * (q >> 2)) + (q & 3);
+            const int up = 32 * c + r, d = u - up - 1;   // d >= 0: c < h0
             const bool ok = d < K && u < ol;
             const float *p = rev ? links + (size_t)(ol - 1 - (u < ol ? u : ol - 1)) * K + d
                                  : links + (size_t)up * K + d;
             v[q] = ok ? __ldg(p) : -INFINITY;
         }
     };
-    for (int sbase = t0; sbase <= t1; sbase += 64) {   // same trip count in every warp: barriers inside
-        const int s0 = sbase + 16 * mt;
-        float acc[4][4];
+    char *ea_hi = reinterpret_cast<char *>(sm.Ea), *ea_lo = ea_hi + kGroupCols * 32 * sizeof(float);
+    char *yb_hi = reinterpret_cast<char *>(sm.Yb), *yb_lo = yb_hi + (size_t)Tpad * 32 * sizeof(float);
+    const uint32_t idesc_full = umma::instr_desc_tf32(kGroupCols, Tpad > 256 ? 256 : Tpad);
+    float cur[8], nxt[8];
+    tile_load(cmin, cur);
+    for (int c = cmin; c < h0; c++) {
+        if (c + 1 < h0) tile_load(c + 1, nxt);   // in flight while block c is staged and multiplied
+        if (c > cmin) {   // the products of block c - 1 have read the tiles
+            if (ok_all && !umma::mbar_wait(sm.mbar, mbar_phase, kUmmaPolls)) ok_all = false;
+            mbar_phase ^= 1u;
+        }
+        // ---- E tile of block c
 #pragma unroll
-        for (int nn = 0; nn < 4; nn++)
+        for (int half = 0; half < 2; half++) {
+            float e[4];
 #pragma unroll
-            for (int q = 0; q < 4; q++) acc[nn][q] = 0.f;
-        float nxt[8];
-        tile_load(cmin, nxt);
-        for (int c = cmin; c < h0; c++) {
-#pragma unroll
-            for (int q = 0; q < 8; q++) {
-                int r, col;
-                tile_rc(q, r, col);
-                const float l2 = nxt[q] * kLog2e;
+            for (int q = 0; q < 4; q++) {
+                const float l2 = cur[4 * half + q] * kLog2e;
                 strip_note_finite(ir, l2);
-                const int u = 32 * h0 + col;
+                const int r = 4 * (kq0 + 4 * half) + q;
                 ir.all = fminf(ir.all, ((u - 32 * c - r - 1 < K) && u < ol) ? l2 : INFINITY);
-                sm.Et[r * kEtPitch + col] = ex2(l2);
+                e[q] = ex2(l2);
             }
-            __syncthreads();
-            if (c + 1 < h0) tile_load(c + 1, nxt);
-            // scale of the two A rows this lane holds (steps s0 + g8 and s0 + g8 + 8): 2^(sc - g), applied
-            // as two exact power-of-two factors so that an entry only vanishes when it is really below
-            // 2^-126 in the step's unit, i.e. 2^-190 below the largest entry of the finished groups
-            // (the second factor is 1 in the usual case)
-            float as1[2], as2[2];
-#pragma unroll
-            for (int q = 0; q < 2; q++) {
-                const int sx = s0 + g8 + 8 * q;
-                float f1 = 0.f, f2 = 0.f;
-                if (k < gs && sx <= t1) {
-                    const int e = sm.sc[(sx - 1) * nH + c];
-                    int kx = e - sm.g[sx - 1];   // <= 0
-                    if (e != kExpNone && kx >= -252) {
+            float4 hi, lo;
+            tf32_split4(e, hi, lo);
+            const int off = umma::tile_unit_offset(m, kq0 + 4 * half);
+            *reinterpret_cast<float4 *>(ea_hi + off) = hi;
+            *reinterpret_cast<float4 *>(ea_lo + off) = lo;
+        }
+        // ---- scaled rows of block c: row (= step) 8 rg + lane % 8, K chunk kq
+        {
+            const int kq = (lane >> 3) + 4 * (warp & 1);
+            for (int rg = warp >> 1; 8 * rg < Tpad; rg += kStripWarps / 2) {
+                const int sx = 8 * rg + (lane & 7);
+                float y[4] = {0.f, 0.f, 0.f, 0.f};
+                if (sx >= t0 && sx <= t1) {
+                    const int ex = sm.sc[(sx - 1) * nH + c];
+                    const int kx = ex - sm.g[sx - 1];   // <= 0
+                    if (ex != kExpNone && kx >= -252) {
+                        // 2^kx as two exact factors (the second is 1 in the usual case): an entry only
+                        // vanishes when it is really below 2^-126 in the step's unit
                         const int k1 = kx >= -126 ? kx : kx / 2;
-                        f1 = __int_as_float((k1 + 127) << 23);
-                        f2 = __int_as_float((kx - k1 + 127) << 23);
+                        const float f1 = __int_as_float((k1 + 127) << 23), f2 = __int_as_float((kx - k1 + 127) << 23);
+                        const float4 yv = *reinterpret_cast<const float4 *>(sm.Y + (size_t)(sx - 1) * rp + 32 * c + 4 * kq);
+                        y[0] = (yv.x * f1) * f2;
+                        y[1] = (yv.y * f1) * f2;
+                        y[2] = (yv.z * f1) * f2;
+                        y[3] = (yv.w * f1) * f2;
                     }
                 }
-                as1[q] = f1;
-                as2[q] = f2;
+                float4 hi, lo;
+                tf32_split4(y, hi, lo);
+                const int off = umma::tile_unit_offset(sx, kq);
+                *reinterpret_cast<float4 *>(yb_hi + off) = hi;
+                *reinterpret_cast<float4 *>(yb_lo + off) = lo;
             }
-            if (__any_sync(0xffffffffu, as1[0] != 0.f || as1[1] != 0.f)) {
+        }
+        umma::fence_smem_to_async();
+        __syncthreads();
+        if (tid == 4 * 32) {   // one thread of a warp that owns no diagonal block issues the products
+            umma::fence_after_sync();
+            const uint32_t a_hi = umma::smem_u32(ea_hi), a_lo = umma::smem_u32(ea_lo);
+            for (int n0 = 0; n0 < Tpad; n0 += 256) {   // at most 256 steps per instruction
+                const int nn = Tpad - n0 < 256 ? Tpad - n0 : 256;
+                const uint32_t idesc = nn == 256 || Tpad <= 256 ? idesc_full : umma::instr_desc_tf32(kGroupCols, nn);
+                const uint32_t b_hi = umma::smem_u32(yb_hi) + (n0 >> 3) * umma::kRowGroupBytes;
+                const uint32_t b_lo = umma::smem_u32(yb_lo) + (n0 >> 3) * umma::kRowGroupBytes;
+                const uint32_t d = tmem_base + (uint32_t)n0;
 #pragma unroll
-                for (int kk = 0; kk < 4; kk++) {
-                    unsigned ahi[4], alo[4];
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {   // (row g8 + 8 (q & 1), source t4 + 4 (q >> 1))
-                        const int sx = s0 + g8 + 8 * (q & 1);
-                        float a = 0.f;
-                        if (as1[q & 1] != 0.f)
-                            a = (sm.Y[(size_t)(sx - 1) * rp + 32 * c + 8 * kk + t4 + 4 * (q >> 1)] * as1[q & 1]) * as2[q & 1];
-                        ahi[q] = to_tf32(a);
-                        alo[q] = to_tf32(a - __uint_as_float(ahi[q]));
-                    }
-#pragma unroll
-                    for (int nn = 0; nn < 4; nn++) {
-                        const float b0 = sm.Et[(8 * kk + t4) * kEtPitch + 32 * k + 8 * nn + g8];
-                        const float b1 = sm.Et[(8 * kk + t4 + 4) * kEtPitch + 32 * k + 8 * nn + g8];
-                        const unsigned bh0 = to_tf32(b0), bh1 = to_tf32(b1);
-                        const unsigned bl0 = to_tf32(b0 - __uint_as_float(bh0));
-                        const unsigned bl1 = to_tf32(b1 - __uint_as_float(bh1));
-                        mma_tf32(acc[nn], alo, bh0, bh1);
-                        mma_tf32(acc[nn], ahi, bl0, bl1);
-                        mma_tf32(acc[nn], ahi, bh0, bh1);
-                    }
+                for (int kk = 0; kk < umma::kTileK / 8; kk++) {
+                    const uint32_t o = kk * umma::kStepBytes;
+                    umma::mma_tf32(d, umma::smem_desc(a_hi + o), umma::smem_desc(b_hi + o), idesc, c > cmin || kk > 0);
+                    umma::mma_tf32(d, umma::smem_desc(a_hi + o), umma::smem_desc(b_lo + o), idesc, true);
+                    umma::mma_tf32(d, umma::smem_desc(a_lo + o), umma::smem_desc(b_hi + o), idesc, true);
                 }
             }
-            __syncthreads();   // the tile is overwritten in the next round
+            umma::commit(sm.mbar);
         }
-        if (k < gs) {
 #pragma unroll
-            for (int nn = 0; nn < 4; nn++)
-#pragma unroll
-                for (int q = 0; q < 4; q++) {   // (row g8 + 8 (q >> 1), column 2 t4 + (q & 1))
-                    const int sx = s0 + g8 + 8 * (q >> 1);
-                    if (sx <= t1) sm.Pf[sx * kGroupCols + 32 * k + 8 * nn + 2 * t4 + (q & 1)] = acc[nn][q];
-                }
-        }
+        for (int q = 0; q < 8; q++) cur[q] = nxt[q];
     }
+    // the last block's products: the accumulator is complete
+    if (ok_all && !umma::mbar_wait(sm.mbar, mbar_phase, kUmmaPolls)) ok_all = false;
+    mbar_phase ^= 1u;
+    umma::fence_after_sync();
+    return ok_all;
 }
 
 // State a diagonal block carries from one step of its sub-strip to the next.
@@ -284,26 +298,35 @@ struct StripCarry {
     unsigned ybits;    // largest entry of the previous step, as float bits
     unsigned vbits;    // the same before the multiplication by exp(match)
     int sprev;         // the previous step (-1: none yet), for the delayed store of the two maxima
+    float far_next;    // what the finished groups send at the next step (requested from tensor memory)
 };
 
 // One step of a diagonal (triangular) block: sub-strip h = h0 + k of the group, step s.  Three
 // terms meet here, each with its own unit: the block's own sum (unit 2^eo), what the finished
-// groups sent (Pf, unit 2^g[s-1]) and what the group's earlier sub-strips sent (ring accumulator
+// groups sent (phase-1 accumulator, unit 2^g[s-1]) and what the group's earlier sub-strips sent (ring accumulator
 // with its own exponent).  Their magnitudes are known before the own sum is: the maximum of this
 // sub-strip one step ago and warp maxima of the other two, all taken while the own sum is being
 // computed.  The new unit puts the largest of the three near 2^kTargetExp, so that the only
 // things on the step-to-step chain are the shared loads of the previous row, the 32
 // multiply-adds, two scalings and the store; nothing overflows, and what is flushed is 2^-190
 // below the largest term.
+// far_col: tensor-memory address of this warp's 32 lanes of the phase-1 accumulator, column 0 (only
+// meaningful when has_far: the group has finished predecessors); the column of step s + 1 is requested
+// here, at step s.
 __device__ __forceinline__ void strip_diag_step(const StripSmem &sm, const float (&ed)[32], int h, int k, int s,
                                                 int lane, int ol, int W, int rp, int nH, bool want_v,
-                                                StripCarry &cy, StripInputRange &ir) {
+                                                bool has_far, uint32_t far_col, int t1, StripCarry &cy,
+                                                StripInputRange &ir) {
     const int u = 32 * h + lane, pc = 32 * k + lane, ring = (k * kRing + (s & (kRing - 1)));
     // ---- independent of the previous step's result
     const int U = sm.g[s - 1];
     const int en = sm.Pe[ring];
-    const float far = sm.Pf[s * kGroupCols + pc];
-    sm.Pf[s * kGroupCols + pc] = 0.f;   // consumed: clean for the next group
+    float far = 0.f;
+    if (has_far) {   // warp-uniform
+        umma::tmem_ld_wait(cy.far_next);
+        far = cy.far_next;
+        if (s < t1) umma::tmem_ld_col(cy.far_next, far_col + (uint32_t)(s + 1));
+    }
     const float near = sm.Pr[ring * 32 + lane];
     sm.Pr[ring * 32 + lane] = 0.f;      // and the ring entry for the step kRing later
     __syncwarp();
@@ -402,18 +425,25 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
     float *chk = chk_all + (size_t)b * 2 * T + (rev ? T : 0);
     StripSmem sm;
     sm.Y = ssm;
-    sm.Pf = sm.Y + (size_t)T * rp;
-    sm.M = sm.Pf + (size_t)T * kGroupCols;
+    const int Tpad = strip_step_pad(T);
+    sm.Ea = sm.Y + (size_t)T * rp;
+    sm.Yb = sm.Ea + 2 * kGroupCols * 32;
+    sm.M = sm.Yb + (size_t)2 * Tpad * 32;
     sm.Pr = sm.M + kMRing * kGroupCols;
-    sm.Et = sm.Pr + kGroupSubs * kRing * 32;
-    sm.Pe = reinterpret_cast<int *>(sm.Et + 32 * kEtPitch);
+    sm.Pe = reinterpret_cast<int *>(sm.Pr + kGroupSubs * kRing * 32);
     sm.sc = sm.Pe + kGroupSubs * kRing;
     sm.g = sm.sc + T * nH;
     sm.mxy = reinterpret_cast<unsigned *>(sm.g + T);
     sm.mxv = sm.mxy + T * nH;
+    sm.mbar = reinterpret_cast<uint64_t *>((reinterpret_cast<uintptr_t>(sm.mxv + T * nH) + 7) & ~(uintptr_t)7);
+    sm.tmem = reinterpret_cast<uint32_t *>(sm.mbar + 1);
 
+    // tensor memory for the phase-1 accumulator: 128 lanes x Tpad columns (a power of two >= 32 is allocated)
+    int tmem_cols = 32;
+    while (tmem_cols < Tpad) tmem_cols <<= 1;
+    if (warp == 0) umma::tmem_alloc(sm.tmem, tmem_cols);
+    if (tid == 0) umma::mbar_init(sm.mbar, 1);
     for (int x = tid; x < tl * rp; x += kStripThreads) sm.Y[x] = 0.f;
-    for (int x = tid; x < T * kGroupCols; x += kStripThreads) sm.Pf[x] = 0.f;
     for (int x = tid; x < kGroupSubs * kRing * 32; x += kStripThreads) sm.Pr[x] = 0.f;
     for (int x = tid; x < kGroupSubs * kRing; x += kStripThreads) sm.Pe[x] = kExpNone;
     for (int x = tid; x < T * nH; x += kStripThreads) {
@@ -422,7 +452,12 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
         sm.mxv[x] = 0u;
     }
     for (int x = tid; x < T; x += kStripThreads) sm.g[x] = kExpNone;
+    umma::fence_before_sync();
     __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem_base = *sm.tmem;   // lane 0, column 0 of the accumulator
+    uint32_t mbar_phase = 0;   // parity of the next completion of the tensor-core barrier
+    bool tc_ok = true;         // no wait for the tensor core has run out
     StripInputRange ir;
     ir.fin = INFINITY;
     ir.all = K < ol - 1 ? -INFINITY : INFINITY;   // a band narrower than the graph: vertex pairs without a link
@@ -474,7 +509,8 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
         }
         if (kd0 >= 0) strip_load_raw(eb0, links, h0 + ks0, h0 + kd0, lane, K, ol, rev);
         // ---- phase 1: everything the finished groups send into this group
-        if (h0 > 0) strip_bulk_mma(links, sm, h0, gs, t0, t1, tid, K, ol, rp, nH, rev, ir);
+        if (h0 > 0)
+            tc_ok &= strip_bulk_umma(links, sm, h0, t0, t1, tid, K, ol, rp, nH, Tpad, rev, tmem_base, mbar_phase, ir);
         if (kd0 >= 0) strip_exp_block(eb0, h0 + ks0, h0 + kd0, lane, K, ol, ir);
         strip_cp_async_wait_all();
         __syncthreads();
@@ -482,11 +518,18 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
         // tau - k and a square block with sources ks does step tau - ks (its sources were finished
         // in iteration tau - 1, its destination needs the sum in iteration tau - ks + kd).
         StripCarry cy;
-        cy.eo = kExpNone; cy.ybits = 0u; cy.vbits = 0u; cy.sprev = -1;
+        cy.eo = kExpNone; cy.ybits = 0u; cy.vbits = 0u; cy.sprev = -1; cy.far_next = 0.f;
+        uint32_t far_col = 0u;   // this warp's lanes of the phase-1 accumulator (diagonal warp k = warp k: lanes 32k..)
+        const bool has_far = h0 > 0 && t0 <= t1;
         if (kd0 >= 0 && ks0 == kd0) {   // this sub-strip at step t0-1 (non-zero only at step 0)
             const int h = h0 + kd0;
             cy.eo = sm.sc[(t0 - 1) * nH + h];
             cy.ybits = __reduce_max_sync(0xffffffffu, __float_as_uint(sm.Y[(size_t)(t0 - 1) * rp + 32 * h + lane]));
+            if (has_far) {
+                umma::fence_after_sync();
+                far_col = tmem_base + ((uint32_t)(32 * kd0) << 16);
+                umma::tmem_ld_col(cy.far_next, far_col + (uint32_t)t0);
+            }
         }
         for (int tau = t0; tau <= t1 + gs - 1; tau++) {
             if (((tau - t0) & 7) == 0) {   // match values two batches ahead; the batch before them has landed
@@ -496,7 +539,7 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
             if (kd0 >= 0) {
                 const int s = tau - ks0;
                 if (s >= t0 && s <= t1) {
-                    if (ks0 == kd0) strip_diag_step(sm, eb0, h0 + kd0, kd0, s, lane, ol, W, rp, nH, rev, cy, ir);
+                    if (ks0 == kd0) strip_diag_step(sm, eb0, h0 + kd0, kd0, s, lane, ol, W, rp, nH, rev, has_far, far_col, t1, cy, ir);
                     else strip_cross_step(sm, eb0, h0, ks0, kd0, s, lane, rp, nH);
                 }
             }
@@ -507,6 +550,7 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
             sm.mxv[cy.sprev * nH + h0 + kd0] = cy.vbits;
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
+        umma::fence_before_sync();   // the accumulator has been read; the next group's products may overwrite it
         __syncthreads();
         // the group's exponents join the running maxima
         for (int s = t0 - 1 + tid; s <= t1; s += kStripThreads) {
@@ -519,7 +563,7 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
         }
         __syncthreads();
     }
-    if (ir.fin < kMinLog2Input) atomicOr(flag + b, kFlagTiny);
+    if (ir.fin < kMinLog2Input || !tc_ok) atomicOr(flag + b, kFlagTiny);   // either way: redone by the exact kernels
     if (ir.all == -INFINITY) atomicOr(flag + b, kFlagHole);
 
     // ---- write the rows out: log2 values relative to one fp64 offset per row
@@ -557,6 +601,10 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
         const double z2 = (y > 0.f && e != kExpNone) ? (double)lg2(y) + (double)e : (y != y ? (double)y : -INFINITY);
         offs[2 * T + (rev ? 1 : 0)] = z2;
         if (rev) loss[b] = (float)(z2 * kLn2d);
+    }
+    if (warp == 0) {   // every read of the accumulator finished before the last barrier of the group loop
+        __syncwarp();
+        umma::tmem_dealloc(tmem_base, tmem_cols);
     }
 }
 
