@@ -611,7 +611,8 @@ def main():
     h2d_full = sum(t.numel() * t.element_size() for t in host)
     # the links go over PCIe without their padding (host_io.upload_links): row i of the band has only
     # output_length - 1 - i real entries, nothing reads the rest
-    h2d = (h2d_full - host[1].numel() * 4 + host_io.upload_links_bytes(B, L_GRAPH, K, max_ol))
+    links_bytes = host_io.upload_links_bytes(B, L_GRAPH, K, max_ol, pinned=True)
+    h2d = h2d_full - host[1].numel() * 4 + links_bytes
     d2h = 4 * 8
     stats_host = torch.empty(4, dtype=torch.float64).pin_memory()
 

@@ -4,14 +4,63 @@
 // entries; the rest of the [L,K] band (about half of it when K = L-1) is -inf padding that no kernel
 // of this library ever reads (every link access is guarded by "destination < output_length").  A
 // caller that feeds the ops from HOST memory (the reference's host-side callers never do: its model
-// produces the links on the device) pays PCIe time for that padding.  dat_upload_links copies the
-// staircase that covers the real entries instead: rows in blocks of kRowBlock, each block as one
-// strided 3-D copy over all sentences, cut at the longest row of the block.
+// produces the links on the device) pays PCIe time for that padding.  dat_upload_links moves only the
+// real entries.  When the host buffer is page-locked (and therefore mapped into the device's address
+// space) a small kernel PULLS them: one warp per band row reads the row's real prefix straight from
+// host memory in 16-byte units (512 contiguous bytes per warp instruction) and stores it to the device
+// copy (measured: 268 MB of ragged rows at ~38 GB/s, against ~41 GB/s x 284 MB for the copy engines'
+// staircase below and 55 GB/s x 535 MB for the whole band; splitting the rows between the two made no
+// difference).  For pageable memory it falls back to the staircase of kRowBlock-row blocks, each block one strided 3-D copy over all sentences, cut
+// at the longest row of the block.
 #include "dat_common.cuh"
 
 namespace dat {
 constexpr int kRowBlock = 32;
+constexpr int kPullThreads = 256;
+constexpr int kPullBlocks = 96;
+
+// One warp per band row (b, i), i < n - 1: copies the 16-byte units that cover the row's n - 1 - i real
+// entries (at most translen).  src and dst have the same alignment modulo 16; the units may reach a few
+// bytes into the padding on either side of the prefix, which is copied like everything else.
+__global__ void __launch_bounds__(kPullThreads)
+upload_links_pull_kernel(const float *__restrict__ src, float *__restrict__ dst, int B, int L, int K, int n) {
+    const int lane = threadIdx.x & 31;
+    const long long nwarps = (long long)gridDim.x * (kPullThreads / 32);
+    const int per = n - 1;   // rows with a successor, in every sentence
+    const long long rows = (long long)B * per;
+    const uintptr_t base = reinterpret_cast<uintptr_t>(src);
+    const uintptr_t total = (uintptr_t)B * L * K * sizeof(float);
+    const ptrdiff_t shift = reinterpret_cast<const char *>(dst) - reinterpret_cast<const char *>(src);
+    for (long long w = (long long)blockIdx.x * (kPullThreads / 32) + (threadIdx.x >> 5); w < rows; w += nwarps) {
+        const int b = (int)(w / per), i = (int)(w - (long long)b * per);
+        int len = n - 1 - i;
+        len = len < K ? len : K;
+        const uintptr_t lo = ((uintptr_t)b * L + i) * (uintptr_t)K * sizeof(float);
+        uintptr_t a0 = (base + lo) & ~(uintptr_t)15;
+        uintptr_t a1 = (base + lo + (uintptr_t)len * sizeof(float) + 15) & ~(uintptr_t)15;
+        if (a0 < base) a0 = base;                    // base itself is 16-byte aligned (checked by the caller)
+        if (a1 > base + total) a1 = base + total;
+        const int units = (int)((a1 - a0) >> 4);     // <= translen / 4 + 2
+        // every lane requests all its units before it stores any of them
+        uint4 v[4];
+        int k = lane;
+        for (; k + 96 < units; k += 128) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) v[q] = ld_stream16(reinterpret_cast<const void *>(a0 + ((uintptr_t)(k + 32 * q) << 4)));
+#pragma unroll
+            for (int q = 0; q < 4; q++)
+                *reinterpret_cast<uint4 *>(reinterpret_cast<char *>(a0 + ((uintptr_t)(k + 32 * q) << 4)) + shift) = v[q];
+        }
+#pragma unroll
+        for (int q = 0; q < 4; q++)
+            if (k + 32 * q < units) v[q] = ld_stream16(reinterpret_cast<const void *>(a0 + ((uintptr_t)(k + 32 * q) << 4)));
+#pragma unroll
+        for (int q = 0; q < 4; q++)
+            if (k + 32 * q < units)
+                *reinterpret_cast<uint4 *>(reinterpret_cast<char *>(a0 + ((uintptr_t)(k + 32 * q) << 4)) + shift) = v[q];
+    }
 }
+}  // namespace dat
 
 extern "C" {
 
@@ -37,6 +86,20 @@ int dat_upload_links(const float *host_links, float *dev_links, int bsz, int pre
     if (bsz == 0) return DAT_OK;
     DAT_REQUIRE(host_links && dev_links, DAT_ERR_BAD_ARG, "dat_upload_links: null pointer");
     const int n = max_output_length < prelen ? max_output_length : prelen;
+    if (n < 2) return DAT_OK;
+    {
+        // page-locked host memory is visible to kernels: pull the rows' real prefixes
+        void *mapped = nullptr;
+        const bool pinned = cudaHostGetDevicePointer(&mapped, const_cast<float *>(host_links), 0) == cudaSuccess &&
+                            mapped != nullptr;
+        if (!pinned) cudaGetLastError();
+        if (pinned && (reinterpret_cast<uintptr_t>(mapped) & 15) == 0 &&
+            (reinterpret_cast<uintptr_t>(dev_links) & 15) == 0) {
+            upload_links_pull_kernel<<<kPullBlocks, kPullThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+                static_cast<const float *>(mapped), dev_links, bsz, prelen, translen, n);
+            return check_launch("dat_upload_links");
+        }
+    }
     const size_t pitch = (size_t)translen * sizeof(float);
     for (int r0 = 0; r0 < n - 1; r0 += kRowBlock) {
         const int rows = n - 1 - r0 < kRowBlock ? n - 1 - r0 : kRowBlock;

@@ -3,8 +3,9 @@
 DA-Transformer produces ``links`` on the device, so the reference never moves them over PCIe; a
 caller that does keep them in host memory (a data-loading or serving process in front of the ops)
 should not pay for the half of the band that is padding.  ``upload_links`` moves only the entries a
-graph can have (``dat_upload_links``); everything else of the device tensor is left untouched, which
-is safe because no op of this package reads a link whose destination is not below ``output_length``.
+graph can have (``dat_upload_links``: a kernel that reads page-locked host memory row by row, or
+strided copies for pageable memory); the rest of the device tensor is left as it is, which is safe
+because no op of this package reads a link whose destination is not below ``output_length``.
 """
 import torch
 
@@ -13,9 +14,14 @@ from ._native import check, lib, ptr, stream_ptr
 __all__ = ["upload_links", "upload_links_bytes"]
 
 
-def upload_links_bytes(bsz, prelen, translen, max_output_length):
-    """Bytes ``upload_links`` moves for these sizes."""
-    return int(lib().dat_upload_links_bytes(int(bsz), int(prelen), int(translen), int(max_output_length)))
+def upload_links_bytes(bsz, prelen, translen, max_output_length, pinned=True):
+    """Bytes ``upload_links`` moves over the bus for these sizes: the real entries of every row when the
+    source is page-locked (the rows' prefixes, each rounded to 16-byte units by the copying kernel:
+    at most 32 bytes more per row), the 32-row staircase that covers them otherwise."""
+    n = min(int(max_output_length), int(prelen))
+    if not pinned:
+        return int(lib().dat_upload_links_bytes(int(bsz), int(prelen), int(translen), n))
+    return int(bsz) * sum(min(int(translen), n - 1 - i) * 4 for i in range(max(n - 1, 0)))
 
 
 def upload_links(host_links, out, max_output_length=None):

@@ -319,11 +319,13 @@ int dat_viterbi_decode(const float *links_square, const float *unreduced_logits,
 /*
  * Host-to-device copy of band links [bsz,prelen,translen] that skips the padding (no counterpart in the
  * reference, whose callers keep the links on the device): row i of a graph with n vertices has n-1-i
- * real entries, the rest is -inf that no entry point of this library reads.  Copies, for all
- * sentences at once, the staircase of 32-row blocks that covers the entries a graph of
- * max_output_length vertices can have; the other bytes of dev_links are left as they are.
- * host_links should be page-locked for the copies to be asynchronous.  Enqueued on `stream`.
- * dat_upload_links_bytes: the number of bytes that call moves (for accounting).
+ * real entries, the rest is -inf that no entry point of this library reads.  Moves, for all sentences,
+ * the entries a graph of max_output_length vertices can have; the other bytes of dev_links are left as
+ * they are (give or take a few bytes of padding next to the real entries).  Page-locked host memory
+ * (cudaHostAlloc / cudaHostRegister, 16-byte aligned) is read directly by a kernel on `stream`, row by
+ * row; pageable memory goes through strided copies of 32-row blocks, each cut at its longest row.
+ * dat_upload_links_bytes: an upper bound of the bytes that call moves over the bus (the staircase's
+ * count; the kernel moves the rows' exact prefixes rounded to 16 bytes).
  */
 size_t dat_upload_links_bytes(int bsz, int prelen, int translen, int max_output_length);
 int dat_upload_links(const float *host_links, float *dev_links, int bsz, int prelen, int translen,
