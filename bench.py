@@ -438,6 +438,7 @@ def main():
             self.ol, self.tl = dev_all[2][:B].clone(), dev_all[3][:B].clone()
             self.gout = (-1.0 / (self.tl.double() * (B * world))).float()   # d(-(loss/tl).mean())/d loss
             self.align_stream = torch.cuda.Stream(device=dev)
+            self.reducer = ddist.OverlappedStatsReducer(dev)
             self.graph, self.out, self.mode = None, None, "eager"
             if not args.eager:
                 try:
@@ -478,7 +479,8 @@ def main():
             else:
                 self.graph.replay()
                 out = self.out
-            return ddist.all_reduce_stats(out[0])
+            # the 32-byte all-reduce runs on a side stream behind this step only; the next step does not wait for it
+            return self.reducer.submit(out[0])
 
         def regions(self, steps, repeats, warmup):
             """`repeats` timed regions of `steps` steps; each bracketed by barrier + synchronize, timed
@@ -493,6 +495,7 @@ def main():
                 t0.record()
                 for _ in range(steps):
                     stats = self.run()
+                self.reducer.wait()          # every all-reduce of the region ends inside it
                 t1.record()
                 barrier()
                 out.append(max_over_ranks(t0.elapsed_time(t1)))
@@ -769,13 +772,14 @@ def main():
         # fallback), loss backward (3: grad_match, product-form grad_links, exact fallback), statistics (1)
         "gpu_launches": 9 * args.steps * args.repeats,
         "roofline": {
-            "kernel": ("dag_loss forward = dag_strip_sweep_kernel (alpha and beta recursions, one CTA each, "
-                       "exp(links) blocks held in registers) with its order, check and fallback launches"),
+            "kernel": ("dag_loss forward = dag_strip_sweep_kernel (alpha and beta recursions, one CTA each; finished "
+                       "vertex groups through tcgen05 3xTF32 products, blocks inside a group as FFMAs on "
+                       "exp(links) held in registers) with its order, check and fallback launches"),
             "bound": "mufu", "achieved": sweep_rate / 1e9, "peak": mufu_peak / 1e9, "unit": "Gexp/s",
             "frac": sweep_rate / mufu_peak,
             # dram__bytes_read+write of dag_strip_sweep_kernel from the ncu capture summarised in
-            # profiles/dag_strip_sweep_c4_148sent.md (108.7 MB for 148 sentences), scaled by sentences
-            "traffic": 108.7e6 / 148 * B,
+            # profiles/dag_strip_sweep_c4_148sent.md (108.5 MB for 148 sentences), scaled by sentences
+            "traffic": 108.5e6 / 148 * B,
             "peak_kind": "measured on this device by the ex2 probe just before the timed regions",
             "nominal_peak": 16 * sm_count * peaks.get("sm_max_mhz", 1965.0) * 1e6 / 1e9,
             "algorithmic_exps_per_launch": sweep_exps, "kernel_ms": sweep_ms,
@@ -785,7 +789,7 @@ def main():
         },
         "roofline_shipped": {
             "what": ("work dag_strip_sweep_kernel executes per launch: 32x32 blocks inside a 128-vertex group as "
-                     "fp32 FMAs, all other blocks as 3xTF32 tensor-core products (mma.sync m16n8k8)"),
+                     "fp32 FMAs, all other blocks as 3xTF32 tensor-core products (tcgen05.mma kind::tf32, M=128, accumulator in tensor memory)"),
             "ffma_executed": ffma_exec, "ffma_rate_tfma_s": ffma_exec / (sweep_ms * 1e-3) / 1e12,
             "ffma_peak_tfma_s": ffma_peak / 1e12, "ffma_frac": ffma_exec / (sweep_ms * 1e-3) / ffma_peak,
             "tf32_fma_executed": mma_exec, "tf32_rate_tfma_s": mma_exec / (sweep_ms * 1e-3) / 1e12,
@@ -919,6 +923,63 @@ def extra_legs(torch, dev, ev, workloads, dag_loss, dag_best_alignment, dag_logs
                        "flagged_sentences": int(flagged[0].item()),
                        "exact_backward_only_sentences": int(flagged[1].item()),
                        "finite_losses": int(torch.isfinite(res).sum().item())}
+    last_status()
+    del m, l, pk, alpha, beta, scratch
+    torch.cuda.empty_cache()
+
+    # The callers either side of the path: links from per-head scores (HBM-bound: the scores are read
+    # once, the band written once; the backward writes the dense gradient once) and the decode-side DPs.
+    from da_transformer_b200 import dag_links_from_heads, dag_node_passing_prob, dag_viterbi_decode
+
+    Bh, Lh, H = 64, 512, 8
+    K = Lh - 1
+    g = torch.Generator(device=dev)
+    g.manual_seed(workloads.BASE_SEED + 2)
+    content = torch.randn(Bh, Lh, Lh, H, device=dev, generator=g).requires_grad_()
+    gates = torch.log_softmax(torch.randn(Bh, Lh, H, device=dev, generator=g), -1).requires_grad_()
+    nonpad = torch.ones(Bh, Lh, dtype=torch.bool, device=dev)
+    glinks = torch.randn(Bh, Lh, K, device=dev, generator=g)
+    peaks, peak_kind = measured_peaks()
+    peak = peaks.get("hbm_gbs", 6650.0)
+
+    def lh_fwd():
+        with torch.no_grad():
+            dag_links_from_heads(content, gates, nonpad_mask=nonpad, max_transition_length=K)
+
+    lk = dag_links_from_heads(content, gates, nonpad_mask=nonpad, max_transition_length=K)
+
+    def lh_bwd():
+        torch.autograd.grad(lk, [content, gates], grad_outputs=glinks, retain_graph=True)
+
+    f_ms, _, _ = time_median(lh_fwd, 10)
+    b_ms, _, _ = time_median(lh_bwd, 10)
+    tri = Bh * (Lh * (Lh - 1) // 2) * H * 4.0          # the successors' scores of every vertex
+    band = Bh * Lh * K * 4.0
+    dense = Bh * Lh * Lh * H * 4.0
+    f_bytes = tri + band + Bh * Lh * H * 4.0
+    b_bytes = tri + band + dense + 2 * Bh * Lh * H * 4.0
+    out["links_from_heads"] = {
+        "workload": f"log_multi_content [{Bh},{Lh},{Lh},{H}] fp32 -> band links [{Bh},{Lh},{K}], forward; backward "
+                    f"writes the dense [B,L,L,H] gradient",
+        "fwd_ms": f_ms, "bwd_ms": b_ms, "fwd_algorithmic_bytes": f_bytes, "bwd_algorithmic_bytes": b_bytes,
+        "fwd_gbs": f_bytes / (f_ms * 1e-3) / 1e9, "bwd_gbs": b_bytes / (b_ms * 1e-3) / 1e9,
+        "fwd_frac": f_bytes / (f_ms * 1e-3) / 1e9 / peak, "bwd_frac": b_bytes / (b_ms * 1e-3) / 1e9 / peak,
+        "bound": "hbm", "peak_gbs": peak, "peak_kind": peak_kind}
+    del content, gates, lk, glinks
+    torch.cuda.empty_cache()
+
+    raw = torch.randn(Bh, Lh, Lh, device=dev, generator=g)
+    upper = torch.triu(torch.ones(Lh, Lh, dtype=torch.bool, device=dev), 1)
+    sq = torch.log_softmax(raw.masked_fill(~upper, float("-inf")), -1)
+    sq = sq.masked_fill(~upper, float("-inf")).contiguous()
+    tok_logit = -torch.rand(Bh, Lh, device=dev, generator=g)
+    tok = torch.randint(4, 1000, (Bh, Lh), device=dev, generator=g)
+    olen = torch.full((Bh,), Lh, dtype=torch.long, device=dev)
+    np_ms, _, _ = time_median(lambda: dag_node_passing_prob(sq), 10)
+    vt_ms, _, _ = time_median(lambda: dag_viterbi_decode(sq, (tok_logit, tok), olen, Lh // 4), 10)
+    out["decode"] = {"workload": f"square links [{Bh},{Lh},{Lh}] fp32: node-passing probabilities; Viterbi "
+                                 f"decoding up to {Lh // 4} tokens with back-trace and token collapse",
+                     "node_passing_ms": np_ms, "viterbi_ms": vt_ms}
     last_status()
     return out
 

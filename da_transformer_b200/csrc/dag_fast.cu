@@ -63,6 +63,8 @@ struct FastScratch {
     float *sub;   // [B][2][T][nH]      the same per 32-vertex sub-strip (strip path only)
     int *flag;    // [B]                kFlag* bits, then the verdict
     int *order;   // [B]                sentences sorted by decreasing cost
+    float *hk;    // [B][T + 32]        backward: half the log2 scale of the step's factor product
+    int4 *sel;    // [B]                backward: snapshot of the verdicts (and lengths) the product-form kernel works from
 };
 
 __host__ __device__ inline int strip_row_pitch_hd(int prelen) { return ((prelen + 63) & ~63) + 4; }
@@ -75,8 +77,9 @@ __host__ __device__ inline size_t fast_scratch_bytes(int B, int T, int L, bool w
     size_t c = (size_t)B * 2 * T * sizeof(float);
     size_t f = (size_t)B * sizeof(int) * 2;
     size_t u = (size_t)B * 2 * T * fast_sub_strips(L) * sizeof(float);
+    size_t h = (((size_t)B * (T + 32) * sizeof(float) + 15) & ~(size_t)15) + (size_t)B * sizeof(int4);
     return ((e + 255) & ~(size_t)255) + ((c + 255) & ~(size_t)255) + ((f + 255) & ~(size_t)255) +
-           ((u + 255) & ~(size_t)255) + 256;
+           ((u + 255) & ~(size_t)255) + ((h + 255) & ~(size_t)255) + 256;
 }
 
 static inline FastScratch carve_fast(void *scratch, int B, int T, int L) {
@@ -89,6 +92,9 @@ static inline FastScratch carve_fast(void *scratch, int B, int T, int L) {
     p += (((size_t)B * sizeof(int) * 2) + 255) & ~(size_t)255;
     s.sub = reinterpret_cast<float *>(p);
     p += (((size_t)B * 2 * T * fast_sub_strips(L) * sizeof(float)) + 255) & ~(size_t)255;
+    s.hk = reinterpret_cast<float *>(p);
+    s.sel = reinterpret_cast<int4 *>(p + (((size_t)B * (T + 32) * sizeof(float) + 15) & ~(size_t)15));
+    p += ((((size_t)B * (T + 32) * sizeof(float) + 15) & ~(size_t)15) + (size_t)B * sizeof(int4) + 255) & ~(size_t)255;
     s.esq = reinterpret_cast<float *>(p);   // only present (and only touched) on the tiled path
     return s;
 }
@@ -639,6 +645,10 @@ dag_fast_grad_links_kernel(const float *__restrict__ grad_out, const float *__re
     }
 }
 
+}  // namespace dat
+#include "dag_grad_umma.cuh"
+namespace dat {
+
 // count[0]: sentences the forward handed to the exact kernels; count[1]: sentences whose forward was
 // kept but whose grad_links goes to the exact kernel
 __global__ void dag_fast_flagged_kernel(const int *__restrict__ flag, int32_t *__restrict__ count, int B) {
@@ -721,6 +731,7 @@ int dat_dag_loss_backward_fast(const float *grad_output, const float *alpha, con
                                    target_length, grad_match_all, bsz, tarlen, prelen, st,
                                    "dat_dag_loss_backward_fast(grad_match)"))
         return rc;
+#ifdef DAT_GRAD_LINKS_FFMA
     {
         dim3 grid((prelen + translen + kGT - 1) / kGT, (prelen + kGT - 1) / kGT, bsz);
         const size_t smem = (size_t)(2 * kGK * kGT + tarlen) * sizeof(float);
@@ -730,6 +741,25 @@ int dat_dag_loss_backward_fast(const float *grad_output, const float *alpha, con
                                                             pitch);
         if (int rc = check_launch("dat_dag_loss_backward_fast(grad_links)")) return rc;
     }
+#else
+    {
+        if (cudaFuncSetAttribute(dag_grad_links_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kGuSmemBytes) != cudaSuccess)
+            return check_launch("dat_dag_loss_backward_fast(attr)");
+        const int nC = gu_classes(prelen, translen), nJw = ((kGuTile - 1 + translen) / kGuTile) + 1;
+        const long long ntiles = (long long)bsz * nC;
+        const int grid = (int)(ntiles < di.sm_count ? ntiles : di.sm_count);
+        dag_grad_links_prep_kernel<<<dim3((prelen + 31) / 32, bsz), 256, 0, st>>>(
+            grad_output, offsets, sc.flag, output_length, target_length, sc.hk, sc.sel, grad_links, tarlen, prelen,
+            translen);
+        if (int rc = check_launch("dat_dag_loss_backward_fast(prep)")) return rc;
+        dag_grad_links_umma_kernel<<<grid, kGuThreads, kGuSmemBytes, st>>>(
+            alpha, beta, sc.hk, links, sc.sel, sc.flag, grad_links, tarlen, prelen, translen, nC, nJw,
+            ntiles);
+        if (int rc = check_launch("dat_dag_loss_backward_fast(grad_links)")) return rc;
+        (void)esq; (void)rows; (void)pitch;
+    }
+#endif
     // sentences the forward handed to the exact kernels get the exact backward as well
     return launch_exact_grad_links(grad_output, alpha, beta, offsets, links, output_length,
                                    target_length, grad_links, sc.flag, bsz, tarlen, prelen, translen, st,

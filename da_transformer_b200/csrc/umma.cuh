@@ -78,6 +78,27 @@ __device__ __forceinline__ void tmem_ld_col(float &v, uint32_t taddr) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
     v = __uint_as_float(r);
 }
+// Eight consecutive accumulator columns for the 32 TMEM lanes this warp may touch (asynchronous like
+// tmem_ld_col).
+__device__ __forceinline__ void tmem_ld_col8(float (&v)[8], uint32_t taddr) {
+    uint32_t r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+#pragma unroll
+    for (int k = 0; k < 8; k++) v[k] = __uint_as_float(r[k]);
+}
+// the values may only be used after this (they pass through the wait so that no use is scheduled before it)
+__device__ __forceinline__ void tmem_ld_wait8(float (&v)[8]) {
+    uint32_t r[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) r[k] = __float_as_uint(v[k]);
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])::"memory");
+#pragma unroll
+    for (int k = 0; k < 8; k++) v[k] = __uint_as_float(r[k]);
+}
 __device__ __forceinline__ void tmem_ld_wait(float &v) {
     uint32_t r = __float_as_uint(v);
     asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r)::"memory");

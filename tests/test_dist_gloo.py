@@ -27,8 +27,14 @@ def _worker(rank, world, port, loss_all, tl_all, out):
     try:
         s, e = ddist.shard_bounds(loss_all.numel(), rank, world)
         stats = ddist.sentence_stats(loss_all[s:e], tl_all[s:e])
+        local = stats.clone()
         stats = ddist.all_reduce_stats(stats)
         out[rank] = stats.clone()
+        # the overlapped reducer gives the same numbers and leaves its input alone (on CPU it reduces at once)
+        red = ddist.OverlappedStatsReducer(device="cpu")
+        got = red.submit(local)
+        red.wait()
+        assert torch.equal(got, stats) and got.data_ptr() != local.data_ptr()
     finally:
         dist.destroy_process_group()
 

@@ -329,3 +329,19 @@ def test_upload_links_moves_the_real_entries_and_the_ops_never_read_the_rest():
         res.append((loss.detach(), gm, gl, path))
     assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1]) and torch.equal(res[0][3], res[1][3])
     assert torch.equal(res[0][2][:, real], res[1][2][:, real])
+
+
+@pytest.mark.gpu
+def test_overlapped_stats_reducer_keeps_every_submission_apart():
+    from da_transformer_b200 import dist as ddist
+
+    dev = torch.device("cuda:0")
+    red = ddist.OverlappedStatsReducer(dev, slots=3)
+    src = torch.zeros(4, dtype=torch.float64, device=dev)
+    got = []
+    for k in range(3):
+        src.fill_(float(k + 1))          # the producer overwrites its buffer every step
+        got.append(red.submit(src))
+    red.wait()
+    torch.cuda.synchronize()
+    assert [float(g[0]) for g in got] == [1.0, 2.0, 3.0]
