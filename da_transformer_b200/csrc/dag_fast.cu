@@ -727,11 +727,15 @@ int dat_dag_loss_backward_fast(const float *grad_output, const float *alpha, con
     // the strip sweep builds no square exp(links) copy: the gradient kernel then exponentiates the band entry
     // it is about to overwrite with the gradient's twin anyway (same address pattern as its store)
     const float *esq = strip_applicable(tarlen, prelen, di) ? nullptr : sc.esq;
+    // grad_match rides in the prep kernel of grad_links when its tensors allow 128-bit accesses
+    const bool match_vec = (prelen & 3) == 0 &&
+                           ((reinterpret_cast<uintptr_t>(alpha) | reinterpret_cast<uintptr_t>(beta) |
+                             reinterpret_cast<uintptr_t>(match_all) | reinterpret_cast<uintptr_t>(grad_match_all)) & 15) == 0;
+#ifdef DAT_GRAD_LINKS_FFMA
     if (int rc = launch_grad_match(grad_output, alpha, beta, offsets, match_all, output_length,
                                    target_length, grad_match_all, bsz, tarlen, prelen, st,
                                    "dat_dag_loss_backward_fast(grad_match)"))
         return rc;
-#ifdef DAT_GRAD_LINKS_FFMA
     {
         dim3 grid((prelen + translen + kGT - 1) / kGT, (prelen + kGT - 1) / kGT, bsz);
         const size_t smem = (size_t)(2 * kGK * kGT + tarlen) * sizeof(float);
@@ -749,9 +753,14 @@ int dat_dag_loss_backward_fast(const float *grad_output, const float *alpha, con
         const int nC = gu_classes(prelen, translen), nJw = ((kGuTile - 1 + translen) / kGuTile) + 1;
         const long long ntiles = (long long)bsz * nC;
         const int grid = (int)(ntiles < di.sm_count ? ntiles : di.sm_count);
-        dag_grad_links_prep_kernel<<<dim3((prelen + 31) / 32, bsz), 256, 0, st>>>(
-            grad_output, offsets, sc.flag, output_length, target_length, sc.hk, sc.sel, grad_links, tarlen, prelen,
-            translen);
+        if (!match_vec)
+            if (int rc = launch_grad_match(grad_output, alpha, beta, offsets, match_all, output_length,
+                                           target_length, grad_match_all, bsz, tarlen, prelen, st,
+                                           "dat_dag_loss_backward_fast(grad_match)"))
+                return rc;
+        dag_grad_links_prep_kernel<<<dim3((tarlen + kGmSteps - 1) / kGmSteps, bsz), 256, 0, st>>>(
+            grad_output, alpha, beta, offsets, match_all, sc.flag, output_length, target_length, grad_match_all,
+            sc.hk, sc.sel, grad_links, tarlen, prelen, translen, match_vec ? 1 : 0);
         if (int rc = check_launch("dat_dag_loss_backward_fast(prep)")) return rc;
         dag_grad_links_umma_kernel<<<grid, kGuThreads, kGuSmemBytes, st>>>(
             alpha, beta, sc.hk, links, sc.sel, sc.flag, grad_links, tarlen, prelen, translen, nC, nJw,

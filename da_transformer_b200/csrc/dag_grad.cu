@@ -46,6 +46,17 @@ dag_grad_match_kernel(const float *__restrict__ grad_out, const float *__restric
     gmatch[x] = out;
 }
 
+// The same, four vertices per thread and kGmSteps target steps per CTA (grad_match_steps_vec, dag_tiles.cuh),
+// for rows that start on 16-byte boundaries (prelen a multiple of 4).
+__global__ void __launch_bounds__(256)
+dag_grad_match_vec_kernel(const float *__restrict__ grad_out, const float *__restrict__ alpha,
+                          const float *__restrict__ beta, const double *__restrict__ offsets,
+                          const float *__restrict__ match, const int64_t *__restrict__ output_length,
+                          const int64_t *__restrict__ target_length, float *__restrict__ gmatch, int T, int L) {
+    grad_match_steps_vec(grad_out, alpha, beta, offsets, match, output_length, target_length, gmatch, T, L,
+                         blockIdx.y, blockIdx.x * kGmSteps);
+}
+
 constexpr int kGlRows = 8;
 constexpr int kGlThreads = 256;
 
@@ -56,12 +67,15 @@ dag_grad_links_kernel(const float *__restrict__ grad_out, const float *__restric
                       const float *__restrict__ beta, const double *__restrict__ offsets,
                       const float *__restrict__ links, const int64_t *__restrict__ output_length,
                       const int64_t *__restrict__ target_length, float *__restrict__ glinks,
-                      const int *__restrict__ select, int T, int L, int K) {
+                      const int *__restrict__ select, int B, int T, int L, int K) {
     extern __shared__ __align__(16) float a_s[];  // [T][kGlRows]: alpha2[t,i] + k_t, -inf when dead
-    const int b = blockIdx.y;
-    if (select != nullptr && select[b] == 0) return;  // done by the product-form kernel
     const int i0 = blockIdx.x * kGlRows;
     const int tid = threadIdx.x;
+    // a CTA takes every gridDim.y-th sentence: with a selection mask most of them are skipped, and a grid of
+    // one CTA per (row block, sentence) would spend its time launching CTAs that return at once
+    for (int b = blockIdx.y; b < B; b += gridDim.y) {
+    if (select != nullptr && select[b] == 0) continue;  // done by the product-form kernel
+    __syncthreads();   // the previous sentence's readers of a_s
     const long long oll = output_length[b], tll = target_length[b];
     const double *offs = offsets + (size_t)b * (2 * T + 2);
     float *out = glinks + (size_t)b * L * K;
@@ -80,7 +94,7 @@ dag_grad_links_kernel(const float *__restrict__ grad_out, const float *__restric
                 const int d = e - u, i = i0 + u;
                 if (d >= 0 && d < K && i < L) out[(size_t)i * K + d] = 0.f;
             }
-        return;
+        continue;
     }
     const int ol = (int)oll, tl = (int)tll;
     const int W = ol - tl + 1;
@@ -133,6 +147,7 @@ dag_grad_links_kernel(const float *__restrict__ grad_out, const float *__restric
             }
         }
     }
+    }   // sentences
 }
 
 }  // namespace dat
@@ -143,10 +158,19 @@ int launch_grad_match(const float *grad_output, const float *alpha, const float 
                       const double *offsets, const float *match_all, const int64_t *output_length,
                       const int64_t *target_length, float *grad_match_all, int bsz, int tarlen,
                       int prelen, cudaStream_t st, const char *who) {
-    dim3 grid((prelen + 255) / 256, tarlen, bsz);
-    dag_grad_match_kernel<<<grid, 256, 0, st>>>(grad_output, alpha, beta, offsets, match_all,
-                                                output_length, target_length, grad_match_all, tarlen,
-                                                prelen);
+    const bool aligned = (prelen & 3) == 0 && ((reinterpret_cast<uintptr_t>(alpha) | reinterpret_cast<uintptr_t>(beta) |
+                                                reinterpret_cast<uintptr_t>(match_all) |
+                                                reinterpret_cast<uintptr_t>(grad_match_all)) & 15) == 0;
+    if (aligned) {
+        dim3 grid((tarlen + kGmSteps - 1) / kGmSteps, bsz);
+        dag_grad_match_vec_kernel<<<grid, 256, 0, st>>>(grad_output, alpha, beta, offsets, match_all, output_length,
+                                                        target_length, grad_match_all, tarlen, prelen);
+    } else {
+        dim3 grid((prelen + 255) / 256, tarlen, bsz);
+        dag_grad_match_kernel<<<grid, 256, 0, st>>>(grad_output, alpha, beta, offsets, match_all,
+                                                    output_length, target_length, grad_match_all, tarlen,
+                                                    prelen);
+    }
     return check_launch(who);
 }
 
@@ -162,9 +186,10 @@ int launch_exact_grad_links(const float *grad_output, const float *alpha, const 
         cudaFuncSetAttribute(dag_grad_links_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
         return check_launch(who);
-    dim3 grid((prelen + kGlRows - 1) / kGlRows, bsz);
+    // with a selection mask few sentences are expected: 64 CTAs per row block share them out
+    dim3 grid((prelen + kGlRows - 1) / kGlRows, select != nullptr && bsz > 64 ? 64 : bsz);
     dag_grad_links_kernel<<<grid, kGlThreads, smem, st>>>(grad_output, alpha, beta, offsets, links,
-                                                         output_length, target_length, grad_links, select,
+                                                         output_length, target_length, grad_links, select, bsz,
                                                          tarlen, prelen, translen);
     return check_launch(who);
 }

@@ -44,16 +44,21 @@ constexpr int kGuPolls = 1 << 20;
 constexpr size_t kGuSmemBytes =
     (size_t)(2 * 4 * kGuOperand + kGuTile * kGuTile) * sizeof(float) + 6 * sizeof(uint64_t) + 16;
 
-// Before the product kernel, one CTA per (sentence, 32 band rows): h_t of every step (zero past the last
-// one, rows padded so that a 32-step chunk may read past T), the snapshot of the verdicts with what a tile
-// needs to know about its sentence, and zeros in every band entry that is not a link of the graph
-// (j >= ol; whole rows from ol - 1 on; everything when there is nothing to add up).
+// Before the product kernel, kGmSteps target steps and a share of the band rows of a sentence per CTA:
+// grad_match of those steps (when the tensors allow the vector form; the caller launches the plain
+// kernel otherwise), h_t of every step (zero past the last one, rows padded so that a 32-step chunk may
+// read past T), the snapshot of the verdicts with what a tile needs to know about its sentence, and zeros
+// in every band entry that is not a link of the graph (j >= ol; whole rows from ol - 1 on; everything when
+// there is nothing to add up).  The zeros are pure stores and the gradient of the match mostly loads, so
+// the two share the memory system better in one kernel than one after the other.
 constexpr int kGuHkPad = umma::kTileK;
 __global__ void __launch_bounds__(256)
-dag_grad_links_prep_kernel(const float *__restrict__ grad_out, const double *__restrict__ offsets_all,
-                           const int *__restrict__ flag, const int64_t *__restrict__ output_length,
-                           const int64_t *__restrict__ target_length, float *__restrict__ hk_all,
-                           int4 *__restrict__ sel, float *__restrict__ glinks, int T, int L, int K) {
+dag_grad_links_prep_kernel(const float *__restrict__ grad_out, const float *__restrict__ alpha,
+                           const float *__restrict__ beta, const double *__restrict__ offsets_all,
+                           const float *__restrict__ match, const int *__restrict__ flag,
+                           const int64_t *__restrict__ output_length, const int64_t *__restrict__ target_length,
+                           float *__restrict__ gmatch, float *__restrict__ hk_all, int4 *__restrict__ sel,
+                           float *__restrict__ glinks, int T, int L, int K, int with_match) {
     const int b = blockIdx.y;
     const long long oll = output_length[b], tll = target_length[b];
     const double *offs = offsets_all + (size_t)b * (2 * T + 2);
@@ -71,24 +76,28 @@ dag_grad_links_prep_kernel(const float *__restrict__ grad_out, const double *__r
             sel[b] = make_int4(verdict != 0 ? 1 : (fin ? 0 : 2), fin ? (int)oll : 0, fin ? (int)tll : 0,
                                __float_as_int(grad_out[b]));
     }
-    if (verdict != 0) return;   // the exact kernel writes every entry of this sentence
-    const int ol = fin ? (int)oll : 0;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int r = warp; r < 32; r += 8) {
-        const int i = 32 * blockIdx.x + r;
-        if (i >= L) break;
-        int d0 = ol - 1 - i;   // first entry that is not a link
-        d0 = d0 < 0 ? 0 : d0;
-        float *row = glinks + ((size_t)b * L + i) * K;
-        // scalar head up to a 16-byte boundary, then 128-bit stores, then the scalar tail
-        int d1 = d0 + (int)(((16u - (unsigned)(reinterpret_cast<uintptr_t>(row + d0) & 15u)) & 15u) >> 2);
-        d1 = d1 < K ? d1 : K;
-        for (int d = d0 + lane; d < d1; d += 32) row[d] = 0.f;
-        const int nv = (K - d1) >> 2;
-        float4 *rv = reinterpret_cast<float4 *>(row + d1);
-        for (int q = lane; q < nv; q += 32) rv[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int d = d1 + 4 * nv + lane; d < K; d += 32) row[d] = 0.f;
+    if (verdict == 0) {   // (the exact kernel writes every entry of the other sentences)
+        const int ol = fin ? (int)oll : 0;
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        const int per = (L + (int)gridDim.x - 1) / (int)gridDim.x;
+        const int iend = per * ((int)blockIdx.x + 1) < L ? per * ((int)blockIdx.x + 1) : L;
+        for (int i = per * (int)blockIdx.x + warp; i < iend; i += 8) {
+            int d0 = ol - 1 - i;   // first entry that is not a link
+            d0 = d0 < 0 ? 0 : d0;
+            float *row = glinks + ((size_t)b * L + i) * K;
+            // scalar head up to a 16-byte boundary, then 128-bit stores, then the scalar tail
+            int d1 = d0 + (int)(((16u - (unsigned)(reinterpret_cast<uintptr_t>(row + d0) & 15u)) & 15u) >> 2);
+            d1 = d1 < K ? d1 : K;
+            for (int d = d0 + lane; d < d1; d += 32) row[d] = 0.f;
+            const int nv = (K - d1) >> 2;
+            float4 *rv = reinterpret_cast<float4 *>(row + d1);
+            for (int q = lane; q < nv; q += 32) rv[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int d = d1 + 4 * nv + lane; d < K; d += 32) row[d] = 0.f;
+        }
     }
+    if (with_match)
+        grad_match_steps_vec(grad_out, alpha, beta, offsets_all, match, output_length, target_length, gmatch, T, L, b,
+                             (int)blockIdx.x * kGmSteps);
 }
 
 __device__ __forceinline__ void gu_split4(const float (&v)[4], float4 &hi, float4 &lo) {
@@ -209,12 +218,16 @@ __device__ __forceinline__ void gu_consume(const GuTileInfo &cur, const GuTileIn
         n_lo = lo;
         n_n = (nwork && j < nxt.ol && hi >= lo) ? hi - lo + 1 : 0;
     }
+    float an[8];   // the sums of the batch after the one at hand, requested a batch ahead
+    if (HAVE) umma::tmem_ld_col8(an, ta);
 #pragma unroll 1
     for (int bt = 0; bt < 8; bt++) {
         float a[8];
         if (HAVE) {
-            umma::tmem_ld_col8(a, ta + 8 * bt);
-            umma::tmem_ld_wait8(a);
+            umma::tmem_ld_wait8(an);
+#pragma unroll
+            for (int k = 0; k < 8; k++) a[k] = an[k];
+            if (bt < 7) umma::tmem_ld_col8(an, ta + 8 * (bt + 1));
         }
 #pragma unroll
         for (int k = 0; k < 8; k++) {

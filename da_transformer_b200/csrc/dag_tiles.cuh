@@ -138,4 +138,50 @@ __device__ __forceinline__ TileGeom tile_geom(int cb, int rb, int lane, int W, i
     return g;
 }
 
+// grad_match_all[b, t, j] = g[b] * 2^(alpha2 + beta2 - match * log2e - Z2) for the steps t0 .. t0 + kGmSteps - 1
+// of sentence b, zeros outside the window: called by all 256 threads of a CTA, four vertices per thread;
+// rows must start on 16-byte boundaries (prelen a multiple of 4, aligned tensors).
+constexpr int kGmSteps = 4;
+__device__ __forceinline__ void grad_match_steps_vec(const float *__restrict__ grad_out, const float *__restrict__ alpha,
+                                                     const float *__restrict__ beta, const double *__restrict__ offsets,
+                                                     const float *__restrict__ match,
+                                                     const int64_t *__restrict__ output_length,
+                                                     const int64_t *__restrict__ target_length,
+                                                     float *__restrict__ gmatch, int T, int L, int b, int t0) {
+    const long long ol = output_length[b], tl = target_length[b];
+    const double *offs = offsets + (size_t)b * (2 * T + 2);
+    bool live = lengths_valid(ol, tl, T, L);
+    double z2 = 0.0;
+    if (live) {
+        z2 = offs[2 * T + 1];
+        live = z2 > -INFINITY && z2 < INFINITY;
+    }
+    const float g = live ? grad_out[b] : 0.f;
+    const int W = (int)(ol - tl) + 1, nv = L >> 2;
+    for (int x = threadIdx.x; x < kGmSteps * nv; x += 256) {
+        const int r = x / nv, j = (x - r * nv) << 2, t = t0 + r;
+        if (t >= T) break;
+        const size_t at = ((size_t)b * T + t) * L + j;
+        float4 out = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live && t < tl && j + 3 >= t && j < t + W) {
+            const float k = (float)(offs[t] + offs[T + t] - z2);
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(alpha + at));
+            const float4 bb = __ldg(reinterpret_cast<const float4 *>(beta + at));
+            const float4 m = __ldg(reinterpret_cast<const float4 *>(match + at));
+            const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {bb.x, bb.y, bb.z, bb.w}, mv[4] = {m.x, m.y, m.z, m.w};
+            float o[4];
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                o[c] = 0.f;
+                if (j + c >= t && j + c < t + W && mv[c] > -INFINITY && mv[c] < INFINITY) {
+                    o[c] = g * ex2((av[c] + bv[c]) + fmaf(-mv[c], kLog2e, k));
+                    if (!(o[c] == o[c])) o[c] = 0.f;
+                }
+            }
+            out = make_float4(o[0], o[1], o[2], o[3]);
+        }
+        *reinterpret_cast<float4 *>(gmatch + at) = out;
+    }
+}
+
 }  // namespace dat
