@@ -525,126 +525,6 @@ dag_fast_check_kernel(const double *__restrict__ offsets_all, const float *__res
     }
 }
 
-// ---------------------------------------------------------------------------------------
-// grad_links in product form.  With A'[t][i] = 2^(u_a[t,i] + h_t), B'[t][j] = 2^(u_b[t+1,j] + h_t),
-// h_t = (off_a[t] + off_b[t+1] - log2 Z) / 2, the edge posterior summed over the target steps is
-//     grad_links[i][j-i-1] = g * E[i][j] * sum_t A'[t][i] * B'[t][j]
-// i.e. a [64 x Tn] x [Tn x 64] product per output tile: one exp per stored row entry instead
-// of one per (t, i, j) term.  Only sentences that passed the forward's dynamic-range check
-// take this path (A' * B' <= 2^100 there, so neither factor overflows and a factor that
-// underflows belongs to a posterior below 2^-60); the others are left to the exact kernel.
-// Every band entry of the sentence is written, zeros included.
-// ---------------------------------------------------------------------------------------
-constexpr int kGT = 64;   // output tile edge
-constexpr int kGK = 16;   // target steps per staging round
-
-__global__ void __launch_bounds__(256)
-dag_fast_grad_links_kernel(const float *__restrict__ grad_out, const float *__restrict__ alpha_all,
-                           const float *__restrict__ beta_all, const double *__restrict__ offsets_all,
-                           const float *__restrict__ esq_all, const float *__restrict__ links_all,
-                           const int *__restrict__ flag, const int64_t *__restrict__ output_length,
-                           const int64_t *__restrict__ target_length, float *__restrict__ glinks, int T,
-                           int L, int K, int rows, int pitch) {
-    extern __shared__ __align__(16) float gsm[];
-    float *As = gsm, *Bs = gsm + kGK * kGT, *hk = gsm + 2 * kGK * kGT;  // hk[T]
-    const int b = blockIdx.z;
-    if (flag[b] != 0) return;  // the exact kernel computes this sentence
-    const int i0 = blockIdx.y * kGT, j0 = blockIdx.x * kGT;
-    // band entries of this tile: 0 <= j-i-1 < K for some (i, j)
-    if (j0 + kGT - 2 < i0 || j0 - (i0 + kGT - 1) - 1 >= K) return;
-    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-    const long long oll = output_length[b], tll = target_length[b];
-    const double *offs = offsets_all + (size_t)b * (2 * T + 2);
-    float *out = glinks + (size_t)b * L * K;
-    bool live = lengths_valid(oll, tll, T, L);
-    double z2 = 0.0;
-    if (live) {
-        z2 = offs[2 * T + 1];
-        live = z2 > -INFINITY && z2 < INFINITY && i0 < oll - 1 && j0 < oll;
-    }
-    float acc[4][4];
-#pragma unroll
-    for (int r = 0; r < 4; r++)
-#pragma unroll
-        for (int c = 0; c < 4; c++) acc[r][c] = 0.f;
-    const int ol = (int)oll, tl = (int)tll;
-    if (live) {
-        const int W = ol - tl + 1;
-        const float *al = alpha_all + (size_t)b * T * L;
-        const float *be = beta_all + (size_t)b * T * L;
-        int tlo = j0 - W;
-        if (i0 - W + 1 > tlo) tlo = i0 - W + 1;
-        if (tlo < 0) tlo = 0;
-        int thi = tl - 2;
-        if (i0 + kGT - 1 < thi) thi = i0 + kGT - 1;
-        if (j0 + kGT - 2 < thi) thi = j0 + kGT - 2;
-        for (int t = tlo + tid; t <= thi; t += 256)
-            hk[t] = 0.5f * (float)(offs[t] + offs[T + t + 1] - z2);
-        __syncthreads();
-        for (int t0 = tlo; t0 <= thi; t0 += kGK) {
-            // stage 16 steps x 64 vertices of each factor (4 values per thread and factor)
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-                const int x = tid + 256 * q;
-                const int tt = x >> 6, v = x & 63;
-                const int t = t0 + tt;
-                float av = 0.f, bv = 0.f;
-                if (t <= thi) {
-                    const int i = i0 + v, j = j0 + v;
-                    if (i >= t && i < t + W) av = ex2(__ldg(al + (size_t)t * L + i) + hk[t]);
-                    if (j >= t + 1 && j <= t + W) bv = ex2(__ldg(be + (size_t)(t + 1) * L + j) + hk[t]);
-                }
-                As[x] = av;
-                Bs[x] = bv;
-            }
-            __syncthreads();
-#pragma unroll
-            for (int tt = 0; tt < kGK; tt++) {
-                const float4 a4 = *reinterpret_cast<const float4 *>(As + tt * kGT + 4 * ty);
-                const float4 b4 = *reinterpret_cast<const float4 *>(Bs + tt * kGT + 4 * tx);
-                const float a[4] = {a4.x, a4.y, a4.z, a4.w}, bb[4] = {b4.x, b4.y, b4.z, b4.w};
-#pragma unroll
-                for (int r = 0; r < 4; r++)
-#pragma unroll
-                    for (int c = 0; c < 4; c++) acc[r][c] = fmaf(a[r], bb[c], acc[r][c]);
-            }
-            __syncthreads();
-        }
-    }
-    const float g = live ? grad_out[b] : 0.f;
-    // E[i][j] = exp(link): from the square copy when the forward built one, else straight from the band
-    const float *E = esq_all ? esq_all + (size_t)b * rows * pitch : nullptr;
-    const float *lk = links_all + (size_t)b * L * K;
-#pragma unroll
-    for (int r = 0; r < 4; r++) {
-        const int i = i0 + 4 * ty + r;
-        if (i >= L) continue;
-        float e[4] = {0.f, 0.f, 0.f, 0.f};
-        if (live && i < ol) {
-            if (E) {
-                const float4 e4 = __ldg(reinterpret_cast<const float4 *>(E + (size_t)i * pitch + j0 + 4 * tx));
-                e[0] = e4.x; e[1] = e4.y; e[2] = e4.z; e[3] = e4.w;
-            } else {
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    const int j = j0 + 4 * tx + c, d = j - i - 1;
-                    if (d >= 0 && d < K && j < ol) e[c] = ex2(__ldg(lk + (size_t)i * K + d) * kLog2e);
-                }
-            }
-        }
-#pragma unroll
-        for (int c = 0; c < 4; c++) {
-            const int j = j0 + 4 * tx + c;
-            const int d = j - i - 1;
-            if (d >= 0 && d < K) {
-                float v = g * acc[r][c] * e[c];
-                if (!(v == v)) v = 0.f;
-                out[(size_t)i * K + d] = v;
-            }
-        }
-    }
-}
-
 }  // namespace dat
 #include "dag_grad_umma.cuh"
 namespace dat {
@@ -720,39 +600,23 @@ int dat_dag_loss_backward_fast(const float *grad_output, const float *alpha, con
     DAT_REQUIRE(bsz <= 65535 && tarlen <= 8192, DAT_ERR_UNSUPPORTED,
                 "dat_dag_loss_backward_fast: bsz is limited to 65535 and tarlen to 8192");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int rows = fast_rows(prelen), pitch = fast_pitch(prelen);
     const FastScratch sc = carve_fast(const_cast<void *>(scratch), bsz, tarlen, prelen);
     DeviceInfo di;
     if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
-    // the strip sweep builds no square exp(links) copy: the gradient kernel then exponentiates the band entry
-    // it is about to overwrite with the gradient's twin anyway (same address pattern as its store)
-    const float *esq = strip_applicable(tarlen, prelen, di) ? nullptr : sc.esq;
     // grad_match rides in the prep kernel of grad_links when its tensors allow 128-bit accesses
     const bool match_vec = (prelen & 3) == 0 &&
                            ((reinterpret_cast<uintptr_t>(alpha) | reinterpret_cast<uintptr_t>(beta) |
                              reinterpret_cast<uintptr_t>(match_all) | reinterpret_cast<uintptr_t>(grad_match_all)) & 15) == 0;
-#ifdef DAT_GRAD_LINKS_FFMA
-    if (int rc = launch_grad_match(grad_output, alpha, beta, offsets, match_all, output_length,
-                                   target_length, grad_match_all, bsz, tarlen, prelen, st,
-                                   "dat_dag_loss_backward_fast(grad_match)"))
-        return rc;
     {
-        dim3 grid((prelen + translen + kGT - 1) / kGT, (prelen + kGT - 1) / kGT, bsz);
-        const size_t smem = (size_t)(2 * kGK * kGT + tarlen) * sizeof(float);
-        dag_fast_grad_links_kernel<<<grid, 256, smem, st>>>(grad_output, alpha, beta, offsets, esq, links,
-                                                            sc.flag, output_length, target_length,
-                                                            grad_links, tarlen, prelen, translen, rows,
-                                                            pitch);
-        if (int rc = check_launch("dat_dag_loss_backward_fast(grad_links)")) return rc;
-    }
-#else
-    {
+        // grad_links, product form on the tensor cores, for the sentences whose forward passed the check
         if (cudaFuncSetAttribute(dag_grad_links_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kGuSmemBytes) != cudaSuccess)
             return check_launch("dat_dag_loss_backward_fast(attr)");
         const int nC = gu_classes(prelen, translen), nJw = ((kGuTile - 1 + translen) / kGuTile) + 1;
-        const long long ntiles = (long long)bsz * nC;
-        const int grid = (int)(ntiles < di.sm_count ? ntiles : di.sm_count);
+        DAT_REQUIRE((long long)bsz * nC < (1ll << 30), DAT_ERR_UNSUPPORTED,
+                    "dat_dag_loss_backward_fast: too many tiles (bsz=%d, prelen=%d)", bsz, prelen);
+        const int ntiles = bsz * nC;
+        const int grid = ntiles < di.sm_count ? ntiles : di.sm_count;
         if (!match_vec)
             if (int rc = launch_grad_match(grad_output, alpha, beta, offsets, match_all, output_length,
                                            target_length, grad_match_all, bsz, tarlen, prelen, st,
@@ -766,9 +630,7 @@ int dat_dag_loss_backward_fast(const float *grad_output, const float *alpha, con
             alpha, beta, sc.hk, links, sc.sel, sc.flag, grad_links, tarlen, prelen, translen, nC, nJw,
             ntiles);
         if (int rc = check_launch("dat_dag_loss_backward_fast(grad_links)")) return rc;
-        (void)esq; (void)rows; (void)pitch;
     }
-#endif
     // sentences the forward handed to the exact kernels get the exact backward as well
     return launch_exact_grad_links(grad_output, alpha, beta, offsets, links, output_length,
                                    target_length, grad_links, sc.flag, bsz, tarlen, prelen, translen, st,

@@ -30,9 +30,6 @@
 #pragma once
 
 #include "umma.cuh"
-#ifdef DAT_GU_PROF
-#include <cstdio>
-#endif
 
 namespace dat {
 
@@ -41,8 +38,9 @@ constexpr int kGuGroup = 256;                        // threads per group
 constexpr int kGuThreads = 2 * kGuGroup;
 constexpr int kGuOperand = kGuTile * umma::kTileK;   // floats of one operand chunk (128 rows x 32 steps)
 constexpr int kGuPolls = 1 << 20;
+constexpr int kGuBatch = 8;   // entries a consumer thread works on together (16 and 32 were slower: 316 and 389 us against 259)
 constexpr size_t kGuSmemBytes =
-    (size_t)(2 * 4 * kGuOperand + kGuTile * kGuTile) * sizeof(float) + 6 * sizeof(uint64_t) + 16;
+    (size_t)(2 * 4 * kGuOperand + kGuTile * kGuTile + 2 * kGuOperand) * sizeof(float) + 6 * sizeof(uint64_t) + 16;
 
 // Before the product kernel, kGmSteps target steps and a share of the band rows of a sentence per CTA:
 // grad_match of those steps (when the tensors allow the vector form; the caller launches the plain
@@ -148,11 +146,11 @@ __host__ __device__ inline int gu_classes(int L, int K) {
     for (int ib = 0; ib < nI; ib++) n += gu_class_width(ib, L, nJw);
     return n;
 }
-__device__ __forceinline__ GuTileInfo gu_tile_info(long long tile, int nC, int nJw, const int4 *__restrict__ sel,
+__device__ __forceinline__ GuTileInfo gu_tile_info(int tile, int nC, int nJw, const int4 *__restrict__ sel,
                                                    int L, int K) {
     GuTileInfo ti;
-    int c = (int)(tile % nC), ib = 0;
-    ti.b = (int)(tile / nC);
+    ti.b = tile / nC;
+    int c = tile - ti.b * nC, ib = 0;
     for (int w = gu_class_width(0, L, nJw); c >= w; w = gu_class_width(ib, L, nJw)) {
         c -= w;
         ib++;
@@ -218,39 +216,52 @@ __device__ __forceinline__ void gu_consume(const GuTileInfo &cur, const GuTileIn
         n_lo = lo;
         n_n = (nwork && j < nxt.ol && hi >= lo) ? hi - lo + 1 : 0;
     }
-    float an[8];   // the sums of the batch after the one at hand, requested a batch ahead
-    if (HAVE) umma::tmem_ld_col8(an, ta);
+    // Batches of kGuBatch entries, each in four sweeps (loads, arithmetic, stores, copies): the asynchronous
+    // copy is a compiler barrier for memory accesses, and entry by entry it would keep the next load from
+    // starting; the sums of the batch after the one at hand are requested a batch ahead.
+    constexpr int NB = kGuBatch / 8;
+    float an[NB][8];
+    if (HAVE) {
+#pragma unroll
+        for (int h = 0; h < NB; h++) umma::tmem_ld_col8(an[h], ta + 8 * h);
+    }
 #pragma unroll 1
-    for (int bt = 0; bt < 8; bt++) {
-        float a[8];
+    for (int bt = 0; bt < 64 / kGuBatch; bt++) {
+        float a[NB][8];
         if (HAVE) {
-            umma::tmem_ld_wait8(an);
 #pragma unroll
-            for (int k = 0; k < 8; k++) a[k] = an[k];
-            if (bt < 7) umma::tmem_ld_col8(an, ta + 8 * (bt + 1));
+            for (int h = 0; h < NB; h++) {
+                umma::tmem_ld_wait8(an[h]);
+#pragma unroll
+                for (int k = 0; k < 8; k++) a[h][k] = an[h][k];
+            }
+            if (bt + 1 < 64 / kGuBatch) {
+#pragma unroll
+                for (int h = 0; h < NB; h++) umma::tmem_ld_col8(an[h], ta + kGuBatch * (bt + 1) + 8 * h);
+            }
+        }
+        float v[kGuBatch];
+#pragma unroll
+        for (int k = 0; k < kGuBatch; k++) v[k] = HAVE ? lslot[(kGuBatch * bt + k) * kGuTile] : 0.f;
+        if (HAVE) {
+#pragma unroll
+            for (int k = 0; k < kGuBatch; k++) {
+                v[k] = g * a[k >> 3][k & 7] * ex2(v[k] * kLog2e);
+                if (!(v[k] == v[k])) v[k] = 0.f;
+            }
         }
 #pragma unroll
-        for (int k = 0; k < 8; k++) {
-            const int e = 8 * bt + k;
-            float v = 0.f;
-            if (HAVE) {
-                v = g * a[k] * ex2(lslot[e * kGuTile] * kLog2e);
-                if (!(v == v)) v = 0.f;
-            }
-            if (REAL) {
-                out[eo] = v;
-            } else if ((unsigned)(e - c_lo) < (unsigned)c_n) {
-                out[eo] = v;
-            }
-            if (NREAL) {
-                gu_cp_async4(slot + e * kGuTile * 4, nsrc + eo);
-            } else if ((unsigned)(e - n_lo) < (unsigned)n_n) {
-                gu_cp_async4(slot + e * kGuTile * 4, nsrc + eo);
-            } else {
-                lslot[e * kGuTile] = -INFINITY;
-            }
-            eo += K - 1;
+        for (int k = 0; k < kGuBatch; k++) {
+            const int e = kGuBatch * bt + k;
+            if (REAL || (unsigned)(e - c_lo) < (unsigned)c_n) out[eo + k * (K - 1)] = v[k];
         }
+#pragma unroll
+        for (int k = 0; k < kGuBatch; k++) {
+            const int e = kGuBatch * bt + k;
+            if (NREAL || (unsigned)(e - n_lo) < (unsigned)n_n) gu_cp_async4(slot + e * kGuTile * 4, nsrc + eo + k * (K - 1));
+            else lslot[e * kGuTile] = -INFINITY;
+        }
+        eo += kGuBatch * (K - 1);
     }
 }
 
@@ -258,18 +269,21 @@ __global__ void __launch_bounds__(kGuThreads, 1)
 dag_grad_links_umma_kernel(const float *__restrict__ alpha_all, const float *__restrict__ beta_all,
                            const float *__restrict__ hk_all, const float *__restrict__ links_all,
                            const int4 *__restrict__ sel, int *flag, float *__restrict__ glinks, int T, int L, int K,
-                           int nC, int nJw, long long ntiles) {
+                           int nC, int nJw, int ntiles) {
     extern __shared__ __align__(128) unsigned char gu_raw[];
     float *opnd = reinterpret_cast<float *>(gu_raw);          // [stage][A' hi, A' lo, B' hi, B' lo][kGuOperand]
     float *Lk = opnd + 2 * 4 * kGuOperand;                    // [128 i][128 j] links of the consumers' tile
-    uint64_t *opfree = reinterpret_cast<uint64_t *>(Lk + kGuTile * kGuTile);   // [2] products that read a stage are done
+    float *rawA = Lk + kGuTile * kGuTile;                     // [32 t][128 i] u_a rows of the producers' next chunk
+    float *rawB = rawA + kGuOperand;                          // [32 t][128 j] u_b rows
+    uint64_t *opfree = reinterpret_cast<uint64_t *>(rawB + kGuOperand);   // [2] products that read a stage are done
     uint64_t *full = opfree + 2;                              // [2] an accumulator is complete
     uint64_t *empty = full + 2;                               // [2] an accumulator has been read out (8 warps arrive)
     uint32_t *tslot = reinterpret_cast<uint32_t *>(empty + 2);
     volatile int *dead = reinterpret_cast<volatile int *>(tslot + 1);   // a wait gave up somewhere in the CTA
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // a contiguous range of tiles per CTA: whole sentences, so every CTA gets the same mix of tile classes
-    const long long tile_lo = ntiles * blockIdx.x / gridDim.x, tile_hi = ntiles * (blockIdx.x + 1) / gridDim.x;
+    const int tile_lo = (int)((long long)ntiles * blockIdx.x / gridDim.x),
+              tile_hi = (int)((long long)ntiles * (blockIdx.x + 1) / gridDim.x);
 
     if (warp == 0) umma::tmem_alloc(tslot, 2 * kGuTile);
     if (tid == 32) {
@@ -288,129 +302,159 @@ dag_grad_links_umma_kernel(const float *__restrict__ alpha_all, const float *__r
         const uint32_t idesc = umma::instr_desc_tf32(kGuTile, kGuTile);
         uint32_t ph_op0 = 0u, ph_op1 = 0u, ph_e0 = 0u, ph_e1 = 0u;
         int chunk = 0, nprod = 0;   // operand chunks and product tiles so far
-        bool off = false;           // group-uniform: no tensor-core work any more
         bool go = true;             // the issuing thread's own: false once it gave up on an accumulator
         const int row = tid & (kGuTile - 1), kq0 = tid >> 7;   // this thread's vertex of a tile; its K chunks kq0 + 2 u
-#ifdef DAT_GU_PROF
-        long long p_wait_op = 0, p_load = 0, p_math = 0, p_bar = 0, p_issue = 0, p_dead = 0, p_t, p_total = clock64();
-        int p_tiles = 0;
-#define GU_T0 p_t = clock64();
-#define GU_ACC(x) { long long n_ = clock64(); x += n_ - p_t; p_t = n_; }
-#else
-#define GU_T0
-#define GU_ACC(x)
-#endif
-        GuTileInfo nti;
-        nti.work = false;
-        if (tile_lo < tile_hi) nti = gu_tile_info(tile_lo, nC, nJw, sel, L, K);
-        for (long long tile = tile_lo; tile < tile_hi; tile++) {
-            const GuTileInfo ti = nti;
-            if (tile + 1 < tile_hi) nti = gu_tile_info(tile + 1, nC, nJw, sel, L, K);   // used a tile later
-            if (!ti.work || ti.thi < ti.tlo) continue;
-            const int acc = nprod & 1;
-            nprod++;
-            GU_T0
-            if (!off) off = gu_group_or(1, *dead != 0);
-            GU_ACC(p_dead)
-            if (off) continue;
-            const float *hk = hk_all + (size_t)ti.b * (T + kGuHkPad);
-            // A'[t][i] exists for i in [t, t+W), i.e. t in (i-W, i]; B'[t][j] for j in [t+1, t+W], i.e. t in [j-W, j-1]
-            const int vi = ti.i0 + row, vj = ti.j0 + row;
-            const int a_lo = vi - ti.W + 1, a_hi = vi < L ? (vi < ti.thi ? vi : ti.thi) : -1;
-            const int b_lo = vj - ti.W, b_hi = vj < L ? (vj - 1 < ti.thi ? vj - 1 : ti.thi) : -1;
-            const float *al = alpha_all + (size_t)ti.b * T * L + vi;
-            const float *be = beta_all + ((size_t)ti.b * T + 1) * L + vj;
-            const int nchunks = (ti.thi - ti.tlo + umma::kTileK) / umma::kTileK;
-            bool ok = true;
-            for (int c = 0; c < nchunks; c++, chunk++) {
-                const int s = chunk & 1, t0 = ti.tlo + umma::kTileK * c;
-                float *st = opnd + s * 4 * kGuOperand;
-                if (chunk >= 2) {   // the products of the chunk before last read this stage
-                    if (ok && !umma::mbar_wait(&opfree[s], s ? ph_op1 : ph_op0, kGuPolls)) ok = false;
-                    if (s) ph_op1 ^= 1u; else ph_op0 ^= 1u;
-                }
-                GU_ACC(p_wait_op)
-                // every load of the chunk first (4 units of 4 steps per thread and factor), then the arithmetic
-                float ra[4][4], rb[4][4], hv[4][4];
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int tq = t0 + 4 * (kq0 + 2 * u);
-                    int eo = tq * L;
-#pragma unroll
-                    for (int cc = 0; cc < 4; cc++) {
-                        const int t = tq + cc;
-                        hv[u][cc] = __ldg(hk + t);
-                        ra[u][cc] = (t >= a_lo && t <= a_hi) ? __ldg(al + eo) : -INFINITY;
-                        rb[u][cc] = (t >= b_lo && t <= b_hi) ? __ldg(be + eo) : -INFINITY;
-                        eo += L;
-                    }
-                }
-#ifdef DAT_GU_PROF
-                if (hv[0][0] + ra[0][0] + rb[3][3] + ra[3][3] + hv[3][3] == 123.456f) p_load++;   // waits for the loads
-#endif
-                GU_ACC(p_load)
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int o = umma::tile_unit_offset(row, kq0 + 2 * u);
-                    float va[4], vb[4];
-#pragma unroll
-                    for (int cc = 0; cc < 4; cc++) {
-                        va[cc] = ex2(ra[u][cc] + hv[u][cc]);
-                        vb[cc] = ex2(rb[u][cc] + hv[u][cc]);
-                    }
-                    float4 hi, lo4;
-                    gu_split4(va, hi, lo4);
-                    *reinterpret_cast<float4 *>(reinterpret_cast<char *>(st) + o) = hi;
-                    *reinterpret_cast<float4 *>(reinterpret_cast<char *>(st + kGuOperand) + o) = lo4;
-                    gu_split4(vb, hi, lo4);
-                    *reinterpret_cast<float4 *>(reinterpret_cast<char *>(st + 2 * kGuOperand) + o) = hi;
-                    *reinterpret_cast<float4 *>(reinterpret_cast<char *>(st + 3 * kGuOperand) + o) = lo4;
-                }
-                umma::fence_smem_to_async();
-                GU_ACC(p_math)
-                if (gu_group_or(1, !ok)) {   // also the barrier between the staging and the products
-                    off = true;
-                    break;
-                }
-                GU_ACC(p_bar)
-                if (tid == 0) {
-                    umma::fence_after_sync();
-                    if (go && c == 0 && nprod > 2) {   // the accumulator's previous tile has been read out
-                        go = umma::mbar_wait(&empty[acc], acc ? ph_e1 : ph_e0, kGuPolls);
-                        if (acc) ph_e1 ^= 1u; else ph_e0 ^= 1u;
-                        umma::fence_after_sync();
-                    }
-                    if (go) {
-                        // D[j][i] += B'^T A': the factor along j is the M operand
-                        const uint32_t d = tmem + (uint32_t)(acc * kGuTile);
-                        const uint32_t n_hi = umma::smem_u32(st), n_lo = umma::smem_u32(st + kGuOperand);
-                        const uint32_t m_hi = umma::smem_u32(st + 2 * kGuOperand), m_lo = umma::smem_u32(st + 3 * kGuOperand);
-                        int nk = (ti.thi - t0 + 8) >> 3;   // K steps of 8 that hold a real target step
-                        nk = nk > umma::kTileK / 8 ? umma::kTileK / 8 : nk;
-                        for (int kk = 0; kk < nk; kk++) {
-                            const uint32_t o = kk * umma::kStepBytes;
-                            umma::mma_tf32(d, umma::smem_desc(m_hi + o), umma::smem_desc(n_hi + o), idesc, c > 0 || kk > 0);
-                            umma::mma_tf32(d, umma::smem_desc(m_hi + o), umma::smem_desc(n_lo + o), idesc, true);
-                            umma::mma_tf32(d, umma::smem_desc(m_lo + o), umma::smem_desc(n_hi + o), idesc, true);
-                        }
-                        umma::commit(&opfree[s]);
-                        if (c == nchunks - 1) umma::commit(&full[acc]);
-                    } else {
-                        *dead = 1;   // seen by this group before its next tile, by the consumers when their wait ends
-                    }
-                }
-                GU_ACC(p_issue)
+        // The raw rows of a chunk (32 steps x 128 vertices of u_a and of u_b) are copied asynchronously into
+        // rawA / rawB one chunk ahead; every thread copies exactly the entries it converts itself.
+        float *myA = rawA + row, *myB = rawB + row;
+        struct Chunk {
+            GuTileInfo ti;
+            int tile, c, nchunks;
+            bool valid;
+        };
+        auto advance = [&](Chunk &k) {   // to the next chunk of a tile with a product, in tile order
+            if (k.valid && k.c + 1 < k.nchunks) {
+                k.c++;
+                return;
             }
-            if (off && tid == 0) *dead = 1;
-#ifdef DAT_GU_PROF
-            p_tiles++;
-#endif
+            for (int t = k.tile + 1; t < tile_hi; t++) {
+                const GuTileInfo ti = gu_tile_info(t, nC, nJw, sel, L, K);
+                if (ti.work && ti.thi >= ti.tlo) {
+                    k.ti = ti;
+                    k.tile = t;
+                    k.c = 0;
+                    k.nchunks = (ti.thi - ti.tlo + umma::kTileK) / umma::kTileK;
+                    k.valid = true;
+                    return;
+                }
+            }
+            k.valid = false;
+            k.tile = tile_hi;
+        };
+        // A'[t][i] exists for i in [t, t+W), i.e. t in (i-W, i]; B'[t][j] for j in [t+1, t+W], i.e. t in [j-W, j-1]
+        struct Masks {
+            int a_lo, a_hi, b_lo, b_hi;
+        };
+        auto masks_of = [&](const GuTileInfo &ti) {
+            const int vi = ti.i0 + row, vj = ti.j0 + row;
+            Masks m;
+            m.a_lo = vi - ti.W + 1;
+            m.a_hi = vi < L ? (vi < ti.thi ? vi : ti.thi) : -1;
+            m.b_lo = vj - ti.W;
+            m.b_hi = vj < L ? (vj - 1 < ti.thi ? vj - 1 : ti.thi) : -1;
+            return m;
+        };
+        float hv[4][4], hvn[4][4];
+        auto request = [&](const Chunk &k) {   // the chunk's raw entries and h_t
+            const Masks m = masks_of(k.ti);
+            const int t0 = k.ti.tlo + umma::kTileK * k.c;
+            const float *al = alpha_all + (size_t)k.ti.b * T * L + k.ti.i0 + row;
+            const float *be = beta_all + ((size_t)k.ti.b * T + 1) * L + k.ti.j0 + row;
+            const float *hk = hk_all + (size_t)k.ti.b * (T + kGuHkPad);
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+#pragma unroll
+                for (int cc = 0; cc < 4; cc++) {
+                    const int tl_ = 4 * (kq0 + 2 * u) + cc, t = t0 + tl_;
+                    hvn[u][cc] = __ldg(hk + t);
+                    if (t >= m.a_lo && t <= m.a_hi) gu_cp_async4(umma::smem_u32(myA + tl_ * kGuTile), al + (size_t)t * L);
+                    if (t >= m.b_lo && t <= m.b_hi) gu_cp_async4(umma::smem_u32(myB + tl_ * kGuTile), be + (size_t)t * L);
+                }
+            }
+            gu_cp_async_commit();
+        };
+        Chunk cu;
+        cu.valid = false;
+        cu.tile = tile_lo - 1;
+        cu.c = 0;
+        cu.nchunks = 0;
+        advance(cu);
+        if (cu.valid) request(cu);
+        Chunk pf = cu;
+        if (pf.valid) advance(pf);
+        bool ok = true;
+        int acc = 0;
+        while (cu.valid) {
+            const GuTileInfo &ti = cu.ti;
+            const int c = cu.c;
+            if (c == 0) {
+                acc = nprod & 1;
+                nprod++;
+                if (gu_group_or(1, *dead != 0 || !ok)) break;   // no tensor-core work any more
+            }
+            const int s = chunk & 1, t0 = ti.tlo + umma::kTileK * c;
+            float *st = opnd + s * 4 * kGuOperand;
+            const Masks m = masks_of(ti);
+            // this chunk's raw entries (copied while the previous chunk was converted) into registers ...
+            gu_cp_async_wait_all();
+            float ra[4][4], rb[4][4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+#pragma unroll
+                for (int cc = 0; cc < 4; cc++) {
+                    const int tl_ = 4 * (kq0 + 2 * u) + cc, t = t0 + tl_;
+                    hv[u][cc] = hvn[u][cc];
+                    ra[u][cc] = (t >= m.a_lo && t <= m.a_hi) ? myA[tl_ * kGuTile] : -INFINITY;
+                    rb[u][cc] = (t >= m.b_lo && t <= m.b_hi) ? myB[tl_ * kGuTile] : -INFINITY;
+                }
+            }
+            // ... and the next chunk's on their way
+            if (pf.valid) request(pf);
+            if (chunk >= 2) {   // the products of the chunk before last read this stage
+                if (ok && !umma::mbar_wait(&opfree[s], s ? ph_op1 : ph_op0, kGuPolls)) ok = false;
+                if (s) ph_op1 ^= 1u; else ph_op0 ^= 1u;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int o = umma::tile_unit_offset(row, kq0 + 2 * u);
+                float va[4], vb[4];
+#pragma unroll
+                for (int cc = 0; cc < 4; cc++) {
+                    va[cc] = ex2(ra[u][cc] + hv[u][cc]);
+                    vb[cc] = ex2(rb[u][cc] + hv[u][cc]);
+                }
+                float4 hi, lo4;
+                gu_split4(va, hi, lo4);
+                *reinterpret_cast<float4 *>(reinterpret_cast<char *>(st) + o) = hi;
+                *reinterpret_cast<float4 *>(reinterpret_cast<char *>(st + kGuOperand) + o) = lo4;
+                gu_split4(vb, hi, lo4);
+                *reinterpret_cast<float4 *>(reinterpret_cast<char *>(st + 2 * kGuOperand) + o) = hi;
+                *reinterpret_cast<float4 *>(reinterpret_cast<char *>(st + 3 * kGuOperand) + o) = lo4;
+            }
+            umma::fence_smem_to_async();
+            if (gu_group_or(1, !ok)) break;   // also the barrier between the staging and the products
+            if (tid == 0) {
+                umma::fence_after_sync();
+                if (go && c == 0 && nprod > 2) {   // the accumulator's previous tile has been read out
+                    go = umma::mbar_wait(&empty[acc], acc ? ph_e1 : ph_e0, kGuPolls);
+                    if (acc) ph_e1 ^= 1u; else ph_e0 ^= 1u;
+                    umma::fence_after_sync();
+                }
+                if (go) {
+                    // D[j][i] += B'^T A': the factor along j is the M operand
+                    const uint32_t d = tmem + (uint32_t)(acc * kGuTile);
+                    const uint32_t n_hi = umma::smem_u32(st), n_lo = umma::smem_u32(st + kGuOperand);
+                    const uint32_t m_hi = umma::smem_u32(st + 2 * kGuOperand), m_lo = umma::smem_u32(st + 3 * kGuOperand);
+                    int nk = (ti.thi - t0 + 8) >> 3;   // K steps of 8 that hold a real target step
+                    nk = nk > umma::kTileK / 8 ? umma::kTileK / 8 : nk;
+                    for (int kk = 0; kk < nk; kk++) {
+                        const uint32_t o = kk * umma::kStepBytes;
+                        umma::mma_tf32(d, umma::smem_desc(m_hi + o), umma::smem_desc(n_hi + o), idesc, c > 0 || kk > 0);
+                        umma::mma_tf32(d, umma::smem_desc(m_hi + o), umma::smem_desc(n_lo + o), idesc, true);
+                        umma::mma_tf32(d, umma::smem_desc(m_lo + o), umma::smem_desc(n_hi + o), idesc, true);
+                    }
+                    umma::commit(&opfree[s]);
+                    if (c == cu.nchunks - 1) umma::commit(&full[acc]);
+                } else {
+                    *dead = 1;   // seen by this group before its next tile, by the consumers when their wait ends
+                }
+            }
+            chunk++;
+            cu = pf;
+            if (pf.valid) advance(pf);
         }
-#ifdef DAT_GU_PROF
-        if (blockIdx.x == 0 && (tid == 0 || tid == 200))
-            printf("producer tid %d: tiles %d total %lld  dead-bar %lld wait_op %lld load %lld math %lld bar %lld issue %lld\n", tid,
-                   p_tiles, clock64() - p_total, p_dead, p_wait_op, p_load, p_math, p_bar, p_issue);
-#endif
+        if (cu.valid && tid == 0) *dead = 1;   // left the loop early
+        gu_cp_async_wait_all();
     } else {
         // =========================== consumers ===========================
         // thread = column j0 + jl of the tile (a lane of the accumulator), rows i0 + 64 half .. + 63
@@ -419,26 +463,21 @@ dag_grad_links_umma_kernel(const float *__restrict__ alpha_all, const float *__r
         uint32_t ph_f0 = 0u, ph_f1 = 0u;
         int nprod = 0;
         bool off = false;   // group-uniform
-#ifdef DAT_GU_PROF
-        long long c_full = 0, c_cp = 0, c_pass = 0, c_other = 0, p_t, c_total = clock64();
-        int c_tiles = 0;
-#endif
         GuTileInfo none;
         none.b = 0; none.i0 = 0; none.j0 = 0; none.ol = 0; none.W = 0; none.tlo = 0; none.thi = -1;
         none.work = false; none.real = false; none.g = 0.f;
-        long long tile = tile_lo;
+        int tile = tile_lo;
         GuTileInfo cur = none;
         if (tile < tile_hi) cur = gu_tile_info(tile, nC, nJw, sel, L, K);
         // the first tile's links (the pass over a tile that is not there only fetches)
         gu_consume<false, false, false>(none, cur, cur.work, 0u, Lk, half, jl, glinks, links_all, L, K);
         gu_cp_async_commit();
         for (; tile < tile_hi; tile++) {
-            const long long next = tile + 1;
+            const int next = tile + 1;
             GuTileInfo nxt = none;
             if (next < tile_hi) nxt = gu_tile_info(next, nC, nJw, sel, L, K);
             bool have = false;   // the accumulator holds this tile's sums
             const int acc = nprod & 1;
-            GU_T0
             if (cur.work && cur.thi >= cur.tlo) {
                 nprod++;
                 bool ok = !off && *dead == 0;
@@ -455,9 +494,7 @@ dag_grad_links_umma_kernel(const float *__restrict__ alpha_all, const float *__r
                     have = true;
                 }
             }
-            GU_ACC(c_full)
             gu_cp_async_wait_all();   // this thread's links of the tile are in their slots
-            GU_ACC(c_cp)
             const uint32_t ta = tmem + ((uint32_t)(32 * (cw & 3)) << 16) + (uint32_t)(acc * kGuTile + 64 * half);
             const bool nreal = nxt.work && nxt.real;
             if (have) {
@@ -478,17 +515,9 @@ dag_grad_links_umma_kernel(const float *__restrict__ alpha_all, const float *__r
                 gu_consume<false, false, false>(none, nxt, nxt.work, ta, Lk, half, jl, glinks, links_all, L, K);
             }
             gu_cp_async_commit();
-#ifdef DAT_GU_PROF
-            if (have) { GU_ACC(c_pass) c_tiles++; } else { GU_ACC(c_other) }
-#endif
             cur = nxt;
         }
         gu_cp_async_wait_all();
-#ifdef DAT_GU_PROF
-        if (blockIdx.x == 0 && (ctid == 0 || ctid == 200))
-            printf("consumer ctid %d: tiles %d total %lld  full %lld cp %lld pass %lld other %lld\n", ctid, c_tiles,
-                   clock64() - c_total, c_full, c_cp, c_pass, c_other);
-#endif
     }
     umma::fence_before_sync();
     __syncthreads();
