@@ -94,6 +94,7 @@ struct Elem;
 template <>
 struct Elem<float> {
     static constexpr int kVec = 4;
+    static constexpr uint32_t kNegInfWord = 0xff800000u;   // a 32-bit word full of -inf elements
     __device__ static __forceinline__ float to_float(float v) { return v; }
     __device__ static __forceinline__ float from_float(float v) { return v; }
     __device__ static __forceinline__ void unpack(const uint4 &u, float *f) {
@@ -111,6 +112,7 @@ struct Elem<float> {
 template <>
 struct Elem<__half> {
     static constexpr int kVec = 8;
+    static constexpr uint32_t kNegInfWord = 0xfc00fc00u;
     __device__ static __forceinline__ float to_float(__half v) { return __half2float(v); }
     __device__ static __forceinline__ __half from_float(float v) { return __float2half_rn(v); }
     __device__ static __forceinline__ void unpack(const uint4 &u, float *f) {
@@ -137,6 +139,7 @@ struct Elem<__half> {
 template <>
 struct Elem<__nv_bfloat16> {
     static constexpr int kVec = 8;
+    static constexpr uint32_t kNegInfWord = 0xff80ff80u;
     __device__ static __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
     __device__ static __forceinline__ __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
     __device__ static __forceinline__ void unpack(const uint4 &u, float *f) {

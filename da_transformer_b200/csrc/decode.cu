@@ -85,6 +85,8 @@ viterbi_decode_kernel(const float *__restrict__ links_all, const float *__restri
     float *a0 = vsm, *a1 = vsm + Lp;            // alpha of two consecutive steps
     float *lastcol = a1 + Lp;                    // links[j][ol-1]
     float *lg = lastcol + Lp;                    // token log-probabilities of the vertices
+    float *part_v = lg + Lp;                     // [2][Lp] partial winners of a step's columns
+    int *part_i = reinterpret_cast<int *>(part_v + 2 * Lp);
     __shared__ float red_v[kDecWarps];
     __shared__ int red_i[kDecWarps];
     __shared__ float best_score;
@@ -119,7 +121,12 @@ viterbi_decode_kernel(const float *__restrict__ links_all, const float *__restri
         best_len = 0;
         best_vertex = 0;
     }
-    __syncthreads();
+    // A transition matrix as decoding builds it has -inf on and below its diagonal; the recursion then
+    // only needs the candidates i < j (checked once here: any other matrix takes all L candidates).
+    bool dense = false;
+    for (int i = warp; i < L; i += kDecWarps)
+        for (int j = lane; j <= i; j += 32) dense |= !(__ldg(lk + (size_t)i * L + j) == -INFINITY);
+    const bool upper = !__syncthreads_or(dense);
     for (int t = 0; t < max_length; t++) {
         const float *cur = (t & 1) ? a1 : a0;
         float *nxt = (t & 1) ? a0 : a1;
@@ -159,18 +166,81 @@ viterbi_decode_kernel(const float *__restrict__ links_all, const float *__restri
             }
         }
         if (t + 1 == max_length) break;
-        // ---- next step: nxt[j] = max_i cur[i] + links[i][j], first maximum (:737-742)
-        for (int j = tid; j < L; j += kDecThreads) {
-            float bv = -INFINITY;
-            int bi = INT_MAX;
-            bool nan = false;
-            const float *col = lk + j;
-#pragma unroll 4
-            for (int i = 0; i < L; i++) {
-                const float v = cur[i] + __ldg(col + (size_t)i * L);
-                if (v != v) { if (!nan) { nan = true; bv = v; bi = i; } }
-                else if (!nan && v > bv) { bv = v; bi = i; }
+        // ---- next step: nxt[j] = max_i cur[i] + links[i][j], first maximum (:737-742).  With an upper
+        // triangular matrix the candidates i >= j are -inf + cur[i]: they never win, unless cur[i] is +inf or
+        // NaN (the sum is NaN then, and torch.max returns the first NaN), so such a step takes all L.
+        bool odd = false;
+        if (upper)
+            for (int i = tid; i < L; i += kDecThreads) odd |= !(cur[i] < INFINITY);
+        const bool tri = upper && !__syncthreads_or(odd);
+        // The matrix is walked in 32 x 32 tiles (lane = destination j, 32 sources per tile, all of a tile's
+        // loads in flight together, two tiles at a time).  Column block c has c + 1 tiles when the matrix is
+        // triangular, so blocks c and nb-1-c form a pair of nb + 1 tiles, and the two warps of a warp pair
+        // take half of a pair's tiles each: equal work for all 16 warps.  A column's candidates then come
+        // from at most two warps, in index order; part_v / part_i hold the two partial winners.
+        {
+            const int nb = (L + 31) >> 5, npairs = (nb + 1) >> 1;
+            const int wp = warp & (kDecWarps / 2 - 1), hf = warp / (kDecWarps / 2);
+            for (int p = wp; p < npairs; p += kDecWarps / 2) {
+                const int cbA = p, cbB = nb - 1 - p;
+                const int nA = tri ? cbA + 1 : nb, nB = cbB != cbA ? (tri ? cbB + 1 : nb) : 0;
+                const int tot = nA + nB, cut = (tot + 1) >> 1;
+                const int q0 = hf ? cut : 0, q1 = hf ? tot : cut;
+#pragma unroll 1
+                for (int side = 0; side < 2; side++) {
+                    const int cb = side ? cbB : cbA;
+                    if (side && cbB == cbA) break;
+                    int r0 = side ? q0 - nA : q0, r1 = side ? q1 - nA : q1;   // this warp's row blocks of cb
+                    const int nside = side ? nB : nA;
+                    r0 = r0 < 0 ? 0 : r0;
+                    r1 = r1 > nside ? nside : r1;
+                    const int j = 32 * cb + lane;
+                    float bv = -INFINITY;
+                    int bi = INT_MAX;
+                    bool nan = false;
+                    const float *col = lk + (j < L ? j : 0);
+                    for (int rb = r0; rb < r1; rb += 2) {
+                        float v[64];
+                        const bool two = rb + 1 < r1;
+#pragma unroll
+                        for (int u = 0; u < 32; u++) {
+                            const int i = 32 * rb + u;
+                            v[u] = (i < L && j < L && (!tri || i < j)) ? __ldg(col + (size_t)i * L) : -INFINITY;
+                        }
+                        if (two) {
+#pragma unroll
+                            for (int u = 0; u < 32; u++) {
+                                const int i = 32 * (rb + 1) + u;
+                                v[32 + u] = (i < L && j < L && (!tri || i < j)) ? __ldg(col + (size_t)i * L) : -INFINITY;
+                            }
+                        }
+                        const int nu = two ? 64 : 32;
+#pragma unroll
+                        for (int u = 0; u < 64; u++) {
+                            if (u < nu) {
+                                const int i = 32 * rb + u;
+                                const float w = cur[i < L ? i : 0] + v[u];
+                                if (w != w) { if (!nan) { nan = true; bv = w; bi = i; } }
+                                else if (!nan && w > bv) { bv = w; bi = i; }
+                            }
+                        }
+                    }
+                    if (j < L) {
+                        part_v[hf * Lp + j] = bv;
+                        part_i[hf * Lp + j] = bi;
+                    }
+                }
             }
+        }
+        __syncthreads();
+        for (int j = tid; j < L; j += kDecThreads) {
+            float bv = part_v[j];
+            int bi = part_i[j];
+            const float ov = part_v[Lp + j];
+            const int oi = part_i[Lp + j];
+            // the second partial holds the later indices: it wins only with a strictly larger value, or with
+            // the first NaN
+            if (!(bv != bv) && (ov != ov || ov > bv)) { bv = ov; bi = oi; }
             if (bi == INT_MAX) bi = 0;          // every candidate is -inf: torch returns index 0
             trace[(size_t)t * L + j] = bi;
             nxt[j] = joint ? bv + lg[j] : bv;
@@ -243,8 +313,8 @@ int dat_viterbi_decode(const float *links_square, const float *unreduced_logits,
     DAT_REQUIRE(links_square && unreduced_logits && unreduced_tokens && output_length && workspace &&
                     out_tokens && out_length && out_vertices && out_score,
                 DAT_ERR_BAD_ARG, "%s: null pointer", who);
-    DAT_REQUIRE(prelen <= 8192, DAT_ERR_UNSUPPORTED, "%s: prelen=%d exceeds 8192", who, prelen);
-    const size_t smem = (size_t)4 * ((prelen + 31) & ~31) * sizeof(float);
+    DAT_REQUIRE(prelen <= 4096, DAT_ERR_UNSUPPORTED, "%s: prelen=%d exceeds 4096", who, prelen);
+    const size_t smem = (size_t)8 * ((prelen + 31) & ~31) * sizeof(float);
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(viterbi_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
             cudaSuccess)

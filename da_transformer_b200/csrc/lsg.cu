@@ -146,15 +146,25 @@ lsg_fwd_kernel(const T *__restrict__ x, const int64_t *__restrict__ idx, Strides
             }
             online_update<4 * kVec>(m, s, f);
         }
-        for (; v < nvec; v += kLsgThreads) {
+        if (v < nvec) {
+            // the last one to three vectors of this thread, requested together; a vector that does not exist
+            // is one of -inf elements (no contribution to the sum, never an arg-max candidate)
+            const uint4 none = make_uint4(Elem<T>::kNegInfWord, Elem<T>::kNegInfWord, Elem<T>::kNegInfWord,
+                                          Elem<T>::kNegInfWord);
+            const bool p1 = v + kLsgThreads < nvec, p2 = v + 2 * kLsgThreads < nvec;
             uint4 u0 = ld_stream16(xv + v);
-            float f[kVec];
+            uint4 u1 = p1 ? ld_stream16(xv + v + kLsgThreads) : none;
+            uint4 u2 = p2 ? ld_stream16(xv + v + 2 * kLsgThreads) : none;
+            float f[3 * kVec];
             Elem<T>::unpack(u0, f);
+            Elem<T>::unpack(u1, f + kVec);
+            Elem<T>::unpack(u2, f + 2 * kVec);
             if (kArgmax) {
 #pragma unroll
-                for (int i = 0; i < kVec; i++) arg_better(bm, bi, f[i], head + v * kVec + i);
+                for (int i = 0; i < 3 * kVec; i++)
+                    arg_better(bm, bi, f[i], head + (v + (i / kVec) * kLsgThreads) * kVec + (i % kVec));
             }
-            online_update<kVec>(m, s, f);
+            online_update<3 * kVec>(m, s, f);
         }
         // scalar head and tail
         const int tail0 = head + nvec * kVec;
@@ -363,13 +373,22 @@ lsg_bwd_kernel(T *__restrict__ x, const int64_t *__restrict__ idx, Strides3 is,
                 xv[v + q * kLsgThreads] = Elem<T>::pack(f);
             }
         }
-        for (; v < nvec; v += kLsgThreads) {
-            uint4 u0 = xv[v];
-            float f[kVec];
-            Elem<T>::unpack(u0, f);
+        if (v < nvec) {   // the last one to three vectors of this thread, requested together
+            const bool p1 = v + kLsgThreads < nvec, p2 = v + 2 * kLsgThreads < nvec;
+            uint4 u[3];
+            u[0] = xv[v];
+            if (p1) u[1] = xv[v + kLsgThreads];
+            if (p2) u[2] = xv[v + 2 * kLsgThreads];
 #pragma unroll
-            for (int i = 0; i < kVec; i++) f[i] = nG * ex2(fmaf(f[i], kLog2e, c));
-            xv[v] = Elem<T>::pack(f);
+            for (int q = 0; q < 3; q++) {
+                if (q == 0 || (q == 1 ? p1 : p2)) {
+                    float f[kVec];
+                    Elem<T>::unpack(u[q], f);
+#pragma unroll
+                    for (int i = 0; i < kVec; i++) f[i] = nG * ex2(fmaf(f[i], kLog2e, c));
+                    xv[v + q * kLsgThreads] = Elem<T>::pack(f);
+                }
+            }
         }
         if (tid < head)
             xr[tid] = Elem<T>::from_float(nG * ex2(fmaf(Elem<T>::to_float(xr[tid]), kLog2e, c)));
