@@ -18,7 +18,7 @@
 
 namespace dat {
 
-constexpr int kLinksThreads = 256;
+constexpr int kLinksThreads = 128;   // 256 and 64 threads per vertex row were slower (0.25 / 0.26 against 0.22 ms forward)
 
 struct LinksMask {
     const int64_t *bound_end;      // [B, L]: successors j <= bound_end[b,i] (decoding), or null
@@ -108,21 +108,22 @@ links_fwd_kernel(const float *__restrict__ content, const float *__restrict__ lo
     __syncthreads();
     links_head_lse(sm, nj, H, part_m, part_s, lse_s);
     if (head_lse && tid < H) head_lse[row * H + tid] = lse_s[tid];
+    // per head, what is added to a score: (gate - lse) in log2 units; a head whose every score is -inf
+    // (lse = -inf) takes no part
+    if (tid < H) gate_s[tid] = lse_s[tid] > -INFINITY ? (gate_s[tid] - lse_s[tid]) * kLog2e : -INFINITY;
+    __syncthreads();
     float *out = links + row * (size_t)K;
     for (int d = tid; d < K; d += kLinksThreads) {
         float v = -INFINITY;
         if (d < nj) {
-            float m = kNegBig, s = 0.f;
-            for (int h = 0; h < H; h++) {
-                // a head whose every score is -inf has lse = -inf: z is NaN there and is skipped
-                const float z = ((sm[d * H + h] - lse_s[h]) + gate_s[h]) * kLog2e;
-                if (z > m) {
-                    s *= ex2(m - z);
-                    m = z;
-                }
-                if (z == z) s += ex2(z - m);
+            // max over the heads first, then the sum: no rescaling and no branches inside the loops
+            float m = -INFINITY;
+            for (int h = 0; h < H; h++) m = fmaxf(m, fmaf(sm[d * H + h], kLog2e, gate_s[h]));
+            if (m > -INFINITY) {
+                float s = 0.f;
+                for (int h = 0; h < H; h++) s += ex2(fmaf(sm[d * H + h], kLog2e, gate_s[h]) - m);
+                v = (m + lg2(s)) * kLn2;
             }
-            if (s > 0.f && m > 0.5f * kNegBig) v = (m + lg2(s)) * kLn2;
         }
         out[d] = v;
     }

@@ -175,9 +175,10 @@ int dat_dag_loss_fast_flagged(const void *scratch, int32_t *count, int bsz, int 
 /*
  * Backward for a forward done by dat_dag_loss_fast (replaces dag_loss_backward, dag_loss.cpp:20;
  * dag_loss.cu:518-571, like dat_dag_loss_backward).  `scratch` is the forward's scratch,
- * untouched since.  grad_links is computed in product form (one exp per stored row entry, then
- * a small matrix product over the target steps) for the sentences that passed the forward's
- * dynamic-range check and by the exact kernel for the others.
+ * untouched since (the call writes its own working data into it: it is declared const because its
+ * size and meaning for the caller do not change).  grad_links is computed in product form (one exp per
+ * stored row entry, then a matrix product over the target steps on the tensor cores) for the
+ * sentences that passed the forward's dynamic-range check and by the exact kernel for the others.
  */
 int dat_dag_loss_backward_fast(const float *grad_output, const float *alpha, const float *beta,
                                const double *offsets, const float *match_all, const float *links,
