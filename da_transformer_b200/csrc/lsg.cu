@@ -29,6 +29,9 @@ constexpr int kLsgThreads = 256;
 constexpr int kLsgWarps = kLsgThreads / 32;
 constexpr int kBwdUnroll = 4;   // 16-byte vectors in flight per thread in the backward
 constexpr int kFwdStage = 512;  // selected logits staged per row in the forward
+// six forward CTAs per SM (40 registers; five at the compiler's own choice of 44): more rows in flight cover the
+// reductions at the end of a row.  The backward is left at its 64 registers (four CTAs): five or six were slower.
+constexpr int kFwdMinCtas = 6;
 
 struct Strides3 {
     int64_t b, l, s;
@@ -87,7 +90,7 @@ __device__ __forceinline__ void arg_better(float &bm, int &bi, float v, int i) {
 }
 
 template <typename T, bool kArgmax>
-__global__ void __launch_bounds__(kLsgThreads)
+__global__ void __launch_bounds__(kLsgThreads, kFwdMinCtas)
 lsg_fwd_kernel(const T *__restrict__ x, const int64_t *__restrict__ idx, Strides3 is,
                float *__restrict__ sel, Strides3 ss, float *__restrict__ stats,
                int32_t *__restrict__ status, LsgExtras ex, int64_t rows, int L, int S, int V) {
