@@ -823,7 +823,7 @@ def main():
 
 # dram bytes (read + write) of one forward + one backward launch of the gather on C2 bf16 V=32000
 # (profiles/lsg_c2_bf16_v32000.md: measured on [8,1024,32000], traffic proportional to rows)
-GATHER_TRAFFIC_BYTES = 4 * (532.80e6 + 4.44e6 + 536.98e6 + 467.87e6)   # captured on 8 of the 32 sentences
+GATHER_TRAFFIC_BYTES = 4 * (532.76e6 + 5.34e6 + 536.99e6 + 469.23e6)   # captured on 8 of the 32 sentences
 
 
 def extra_legs(torch, dev, ev, workloads, dag_loss, dag_best_alignment, dag_logsoftmax_gather_inplace, DagLossFunc,
