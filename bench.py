@@ -770,7 +770,7 @@ def main():
                 "with_whole_band_copied": {"value": e2e_full_value, "h2d_bytes_per_step": h2d_full}},
         # per step: alignment (1: strip kernel), loss forward (4: order, strip sweep, check, exact
         # fallback), loss backward (3: grad_match, product-form grad_links, exact fallback), statistics (1)
-        "gpu_launches": 9 * args.steps * args.repeats,
+        "gpu_launches": 8 * args.steps * args.repeats,
         "roofline": {
             "kernel": ("dag_loss forward = dag_strip_sweep_kernel (alpha and beta recursions, one CTA each; finished "
                        "vertex groups through tcgen05 3xTF32 products, blocks inside a group as FFMAs on "

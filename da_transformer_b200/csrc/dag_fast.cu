@@ -49,6 +49,8 @@ constexpr int kFlagTiny = 1;            // in: a finite link or in-window match 
 constexpr int kFlagHole = 4;            // in: two vertices of the graph without a (finite) link between them
 constexpr int kFlagRedo = 1;            // out: forward and backward by the exact log-domain kernels
 constexpr int kFlagExactBackward = 2;   // out: forward kept, grad_links by the exact kernel
+constexpr int kFlagBits = 0xffff;        // the kFlag* bits of a sentence's word
+constexpr int kFlagArrival = 1 << 16;    // above them: how many strip-sweep CTAs of the sentence have finished
 
 }  // namespace dat
 #include "dag_strip.cuh"
@@ -459,22 +461,13 @@ dag_fast_sweep_kernel(const float *__restrict__ match_all, const float *__restri
 // The product form of grad_links multiplies factors of size 2^(R_t / 2); beyond kMaxSpreadBackward its
 // factors would underflow where they matter, so those sentences get the exact grad_links kernel.
 constexpr int kCheckThreads = 128;
-__global__ void __launch_bounds__(kCheckThreads)
-dag_fast_check_kernel(const double *__restrict__ offsets_all, const float *__restrict__ chk_all,
-                                      const float *__restrict__ sub_all, int nH,
-                                      const int64_t *__restrict__ output_length,
-                                      const int64_t *__restrict__ target_length, int *__restrict__ flag,
-                                      int32_t *__restrict__ status, int B, int T, int L) {
-    // one CTA of kCheckThreads per sentence, threads over the (step, sub-strip) pairs
-    const int b = blockIdx.x, tid = threadIdx.x;
-    __shared__ float row_s[kCheckThreads / 32];
-    const long long ol = output_length[b], tl = target_length[b];
-    if (!lengths_valid(ol, tl, T, L)) {
-        if (tid == 0) flag[b] = 0;  // nothing to recompute: the loss is -inf by definition
-        return;
-    }
-    const int bits = flag[b];
-    __syncthreads();
+// The check of one sentence by all `nthreads` threads of a CTA (a multiple of 32, at most 512); every thread of
+// the CTA must call it.  `bits`: the kFlag* bits the sweeps left.
+__device__ __forceinline__ void fast_check_sentence(int b, int bits, const double *__restrict__ offsets_all,
+                                                    const float *__restrict__ chk_all, const float *__restrict__ sub_all,
+                                                    int nH, long long ol, long long tl, int *__restrict__ flag,
+                                                    int32_t *__restrict__ status, int T, int tid, int nthreads) {
+    __shared__ float row_s[16];
     if (bits & kFlagTiny) {  // set by the prep or a sweep kernel: an input below 2^kMinLog2Input
         if (tid == 0) {
             flag[b] = kFlagRedo;
@@ -484,13 +477,13 @@ dag_fast_check_kernel(const double *__restrict__ offsets_all, const float *__res
     }
     const double *offs = offsets_all + (size_t)b * (2 * T + 2);
     const float *chk_a = chk_all + (size_t)b * 2 * T, *chk_bb = chk_a + T;
-    const double z2a = offs[2 * T], z2b = offs[2 * T + 1];
+    const double z2a = __ldcg(offs + 2 * T), z2b = __ldcg(offs + 2 * T + 1);
     bool bad = !(z2a > -INFINITY && z2a < INFINITY && z2b > -INFINITY && z2b < INFINITY);
     if (!bad) bad = !(fabs(z2a - z2b) <= 1e-3 * (1.0 + fabs(z2b)));
     const float z2 = (float)z2b;
     float r_row = -INFINITY;
-    for (int t = tid; t + 1 < (int)tl; t += kCheckThreads) {
-        const float r = chk_a[t] + chk_bb[t] - z2;
+    for (int t = tid; t + 1 < (int)tl; t += nthreads) {
+        const float r = __ldcg(chk_a + t) + __ldcg(chk_bb + t) - z2;
         if (!(r <= 1e30f)) bad = true;   // NaN / inf
         r_row = fmaxf(r_row, r);
     }
@@ -501,21 +494,21 @@ dag_fast_check_kernel(const double *__restrict__ offsets_all, const float *__res
         const float *sa = sub_all + (size_t)b * 2 * T * nH, *sb = sa + (size_t)T * nH;
         const int nsub = ((int)ol + 31) >> 5;
         const int pairs = ((int)tl - 1) * nsub;
-        for (int x = tid; x < pairs; x += kCheckThreads) {
+        for (int x = tid; x < pairs; x += nthreads) {
             const int t = x / nsub, h = x - t * nsub;
-            const float a = sa[t * nH + h];
+            const float a = __ldcg(sa + t * nH + h);
             if (!(a > -INFINITY)) continue;
             // vertices 32h .. 32h+31 are the reversed sweep's canonical vertices ol-1-32h-31 .. ol-1-32h
             int ulo = (int)ol - 32 - 32 * h, uhi = (int)ol - 1 - 32 * h;
             ulo = ulo > 0 ? ulo : 0;
-            const float bb = fmaxf(sb[t * nH + (ulo >> 5)], sb[t * nH + (uhi >> 5)]);
+            const float bb = fmaxf(__ldcg(sb + t * nH + (ulo >> 5)), __ldcg(sb + t * nH + (uhi >> 5)));
             if (!(a + bb - z2 <= kMaxSpreadLocal)) bad = true;
         }
     }
     bad = __syncthreads_or(bad);
     if (tid == 0) {
         r_row = row_s[0];
-        for (int w = 1; w < kCheckThreads / 32; w++) r_row = fmaxf(r_row, row_s[w]);
+        for (int w = 1; w < nthreads / 32; w++) r_row = fmaxf(r_row, row_s[w]);
         if (!local) bad |= !(r_row <= kMaxSpread);
         int verdict = 0;
         if (bad) verdict = kFlagRedo;
@@ -523,6 +516,25 @@ dag_fast_check_kernel(const double *__restrict__ offsets_all, const float *__res
         flag[b] = verdict;
         if (verdict == kFlagRedo && status) atomicOr(status, DAT_STATUS_FAST_FALLBACK);
     }
+}
+
+// One CTA per sentence: the check after the tiled sweep (the strip sweep runs it itself, in the CTA of a
+// sentence that finishes second).
+__global__ void __launch_bounds__(kCheckThreads)
+dag_fast_check_kernel(const double *__restrict__ offsets_all, const float *__restrict__ chk_all,
+                                      const float *__restrict__ sub_all, int nH,
+                                      const int64_t *__restrict__ output_length,
+                                      const int64_t *__restrict__ target_length, int *__restrict__ flag,
+                                      int32_t *__restrict__ status, int B, int T, int L) {
+    const int b = blockIdx.x, tid = threadIdx.x;
+    const long long ol = output_length[b], tl = target_length[b];
+    if (!lengths_valid(ol, tl, T, L)) {
+        if (tid == 0) flag[b] = 0;  // nothing to recompute: the loss is -inf by definition
+        return;
+    }
+    const int bits = flag[b] & kFlagBits;
+    __syncthreads();
+    fast_check_sentence(b, bits, offsets_all, chk_all, sub_all, nH, ol, tl, flag, status, T, tid, kCheckThreads);
 }
 
 }  // namespace dat
@@ -713,10 +725,12 @@ int dat_dag_loss_fast(const float *match_all, const float *links, const int64_t 
             loss, status, tarlen, prelen, translen, rows, pitch);
         if (int rc = check_launch("dat_dag_loss_fast(sweep)")) return rc;
     }
-    dag_fast_check_kernel<<<(unsigned)bsz, kCheckThreads, 0, st>>>(
-        offsets, sc.chk, strip_applicable(tarlen, prelen, di) ? sc.sub : nullptr, fast_sub_strips(prelen),
-        output_length, target_length, sc.flag, status, bsz, tarlen, prelen);
-    if (int rc = check_launch("dat_dag_loss_fast(check)")) return rc;
+    if (!strip_applicable(tarlen, prelen, di)) {   // (the strip sweep's CTAs run the check themselves)
+        dag_fast_check_kernel<<<(unsigned)bsz, kCheckThreads, 0, st>>>(offsets, sc.chk, nullptr, fast_sub_strips(prelen),
+                                                                       output_length, target_length, sc.flag, status, bsz,
+                                                                       tarlen, prelen);
+        if (int rc = check_launch("dat_dag_loss_fast(check)")) return rc;
+    }
     // flagged sentences only; all other CTAs return at once
     return launch_exact_sweeps(match_all, links, output_length, target_length, sc.flag, alpha, beta,
                                offsets, loss, status, bsz, tarlen, prelen, translen, 2, st,

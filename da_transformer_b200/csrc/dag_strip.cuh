@@ -35,6 +35,12 @@
 
 namespace dat {
 
+// defined in dag_fast.cu: the a-posteriori check of one sentence, run by the sentence's sweep CTA that finishes second
+__device__ __forceinline__ void fast_check_sentence(int b, int bits, const double *__restrict__ offsets_all,
+                                                    const float *__restrict__ chk_all, const float *__restrict__ sub_all,
+                                                    int nH, long long ol, long long tl, int *__restrict__ flag,
+                                                    int32_t *__restrict__ status, int T, int tid, int nthreads);
+
 constexpr int kStripThreads = 512;
 constexpr int kStripWarps = kStripThreads / 32;
 constexpr int kExpNone = -(1 << 28);   // exponent of a half-strip that is entirely zero
@@ -605,6 +611,18 @@ dag_strip_sweep_kernel(const float *__restrict__ match_all, const float *__restr
     if (warp == 0) {   // every read of the accumulator finished before the last barrier of the group loop
         __syncwarp();
         umma::tmem_dealloc(tmem_base, tmem_cols);
+    }
+    // ---- the check of the sentence, by whichever of its two CTAs finishes second: the arrival count sits
+    // above the flag bits of the sentence's word (cleared before the launch)
+    __shared__ int arrived_before;
+    __threadfence();   // this CTA's rows, maxima and offsets are visible before its arrival is
+    __syncthreads();
+    if (tid == 0) arrived_before = atomicAdd(flag + b, kFlagArrival);
+    __syncthreads();
+    if (arrived_before >= kFlagArrival) {
+        __threadfence();
+        fast_check_sentence(b, arrived_before & kFlagBits, offsets_all, chk_all, sub_all, nH, oll, tll, flag, status, T, tid,
+                            kStripThreads);
     }
 }
 
