@@ -73,6 +73,11 @@ dag_grad_links_kernel(const float *__restrict__ grad_out, const float *__restric
     const int tid = threadIdx.x;
     // a CTA takes every gridDim.y-th sentence: with a selection mask most of them are skipped, and a grid of
     // one CTA per (row block, sentence) would spend its time launching CTAs that return at once
+    if (select != nullptr) {   // nothing selected among this CTA's sentences (the usual case): one look at all of them
+        bool any = false;
+        for (int b = blockIdx.y + (int)gridDim.y * tid; b < B; b += gridDim.y * kGlThreads) any |= select[b] != 0;
+        if (!__syncthreads_or(any)) return;
+    }
     for (int b = blockIdx.y; b < B; b += gridDim.y) {
     if (select != nullptr && select[b] == 0) continue;  // done by the product-form kernel
     __syncthreads();   // the previous sentence's readers of a_s
