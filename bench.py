@@ -431,7 +431,7 @@ def main():
         (the alignment, independent of the loss, is a parallel branch) and replayed, followed by the
         NCCL all-reduce of the statistics."""
 
-        def __init__(self, B):
+        def __init__(self, B, eager=False):
             self.B = B
             self.match = dev_all[0][:B].clone().requires_grad_()
             self.links = dev_all[1][:B].clone().requires_grad_()
@@ -440,7 +440,7 @@ def main():
             self.align_stream = torch.cuda.Stream(device=dev)
             self.reducer = ddist.OverlappedStatsReducer(dev)
             self.graph, self.out, self.mode = None, None, "eager"
-            if not args.eager:
+            if not (args.eager or eager):
                 try:
                     side = torch.cuda.Stream(device=dev)
                     side.wait_stream(torch.cuda.current_stream(dev))
@@ -548,6 +548,14 @@ def main():
     if other is not None:
         other_regions, _ = other.regions(args.steps, args.repeats, args.warmup)
         other_sum = summarise(other_regions, args.steps, other_B)
+    # the same step launched kernel by kernel through the Python front end (what a criterion that does not
+    # capture graphs gets): host time of the ctypes calls and allocations included
+    eager_sum = None
+    if not args.eager and args.sentences is None:
+        eg = Step(B_head, eager=True)
+        eg_regions, _ = eg.regions(args.steps, 3, args.warmup)
+        eager_sum = summarise(eg_regions, args.steps, B_head)
+        del eg
     weak_sum = head_sum if B_head == B_weak else other_sum
     strong_sum = head_sum if B_head == B_strong else other_sum
     if world == 1 and args.sentences is None:
@@ -762,7 +770,7 @@ def main():
             "launch": head.mode,
             "timing": f"{args.repeats} regions of {args.steps} steps, median region / steps",
         },
-        "weak": weak_sum, "strong": strong_sum,
+        "weak": weak_sum, "strong": strong_sum, "eager": eager_sum,
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "regions": len(e2e_regions),
