@@ -8,8 +8,9 @@
 // where the softmax runs over the valid successors of i inside the band (j in (i, i+K], j < L,
 // column allowed by the mask); invalid entries and vertices without any successor are -inf.
 // The reference materialises [B,L,K,H] three times on the way (gather, log_softmax, + gates).
-// Here one CTA owns one vertex (b,i): it stages the H x (valid successors) scores once in shared
-// memory, reduces per head, and writes the K band entries; nothing else touches HBM.
+// Here one warp owns one vertex (b,i) (head counts that are 4, 8, 16 or 32; a CTA per vertex with the
+// scores staged in shared memory otherwise): it streams the H x (valid successors) scores, reduces per
+// head, streams them again from L2 and writes the K band entries; nothing else touches HBM.
 //
 // HBM-bound.  Algorithmic bytes: forward reads the upper triangle of content once
 // (~ B*L*L*H*4 / 2) and writes B*L*K*4; backward reads the same triangle plus the band gradient and
@@ -206,6 +207,230 @@ links_bwd_kernel(const float *__restrict__ grad_links, const float *content,
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// One WARP per vertex row, no shared memory, no CTA barrier: the row's scores are streamed twice with
+// 128-bit loads (the second pass hits L2: a row is at most a few KB), first for the per-head
+// log-sum-exp (or, backward, the per-head sums S_h), then for the outputs.  A 16-byte vector holds four
+// heads of one successor, and with H/4 a power of two a lane always meets the same four heads, so the
+// per-head state lives in registers and is merged across the lanes by shuffles.  Used when H is a
+// multiple of 4 with H/4 in {1, 2, 4, 8}; other head counts take the kernels above.  Rows are dealt so
+// that the warps of a CTA alternate between long and short rows (vertex i and vertex L-1-i).
+// ---------------------------------------------------------------------------------------------------
+constexpr int kLwWarps = 4;
+constexpr int kLwMaxGroups = 8;   // H / 4
+
+__device__ __forceinline__ int links_row_of_slot(int q, int L) { return (q & 1) ? L - 1 - (q >> 1) : (q >> 1); }
+
+template <int G>   // G = H / 4 vectors per successor
+__global__ void __launch_bounds__(kLwWarps * 32)
+links_fwd_warp_kernel(const float *__restrict__ content, const float *__restrict__ log_gates, LinksMask mk,
+                      float *__restrict__ links, float *__restrict__ head_lse, int B, int L, int K) {
+    constexpr int H = 4 * G;
+    constexpr int U = 8;   // vectors a lane has in flight
+    const int lane = threadIdx.x & 31;
+    const int64_t slot = (int64_t)blockIdx.x * kLwWarps + (threadIdx.x >> 5);
+    if (slot >= (int64_t)B * L) return;
+    const int64_t b = slot / L;
+    const int i = links_row_of_slot((int)(slot - b * L), L);
+    const int64_t row = b * L + i;
+    const int jhi = links_jhi(i, L, K, mk, row);
+    const int nj = jhi - i > 0 ? jhi - i : 0;
+    const unsigned char *np = mk.nonpad ? mk.nonpad + b * L + i + 1 : nullptr;
+    const float4 *src = reinterpret_cast<const float4 *>(content + (row * L + i + 1) * (int64_t)H);
+    const int nvec = nj * G;                      // vectors of the row
+    const int g = lane & (G - 1);                 // this lane's head group: heads 4g .. 4g+3
+    const float4 ninf = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    // ---- pass 1: per-head log-sum-exp over the successors (log2 units), U vectors requested at a time
+    float m[4] = {kNegBig, kNegBig, kNegBig, kNegBig}, sum[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int v0 = lane; v0 < nvec; v0 += 32 * U) {
+        float4 c4[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int v = v0 + 32 * u;
+            c4[u] = (v < nvec && !(np && !np[v / G])) ? __ldg(src + v) : ninf;
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const float c[4] = {c4[u].x * kLog2e, c4[u].y * kLog2e, c4[u].z * kLog2e, c4[u].w * kLog2e};
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                if (c[k] > m[k]) {
+                    sum[k] *= ex2(m[k] - c[k]);
+                    m[k] = c[k];
+                }
+                sum[k] += ex2(c[k] - m[k]);
+            }
+        }
+    }
+#pragma unroll
+    for (int o = G; o < 32; o <<= 1) {   // lanes with the same head group
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const float m2 = __shfl_xor_sync(0xffffffffu, m[k], o), s2 = __shfl_xor_sync(0xffffffffu, sum[k], o);
+            lse_merge(m[k], sum[k], m2, s2);
+        }
+    }
+    // lse (natural log) and what a head adds to a score, (gate - lse) in log2 units (-inf: the head takes no part)
+    float kh[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const float lse = (sum[k] > 0.f && m[k] > 0.5f * kNegBig) ? (m[k] + lg2(sum[k])) * kLn2 : -INFINITY;
+        const int h = 4 * g + k;
+        if (head_lse && lane < G) head_lse[row * H + h] = lse;
+        kh[k] = lse > -INFINITY ? (__ldg(log_gates + row * H + h) - lse) * kLog2e : -INFINITY;
+    }
+    // every lane needs all heads' terms: head group gg from lane gg
+    float ka[H];
+#pragma unroll
+    for (int gg = 0; gg < G; gg++) {
+#pragma unroll
+        for (int k = 0; k < 4; k++) ka[4 * gg + k] = __shfl_sync(0xffffffffu, kh[k], gg);
+    }
+    // ---- pass 2: links[d] = logsumexp_h(score[d][h] + gate_h - lse_h), one successor per lane and round,
+    // U2 rounds requested at a time (the scores come from L2 now)
+    constexpr int U2 = G >= 4 ? 2 : 4;
+    float *out = links + row * (int64_t)K;
+    for (int d0 = lane; d0 < K; d0 += 32 * U2) {
+        float4 c4[U2][G];
+#pragma unroll
+        for (int u = 0; u < U2; u++) {
+            const int d = d0 + 32 * u;
+            const bool live = d < nj && !(np && !np[d]);
+#pragma unroll
+            for (int gg = 0; gg < G; gg++) c4[u][gg] = live ? __ldg(src + d * G + gg) : ninf;
+        }
+#pragma unroll
+        for (int u = 0; u < U2; u++) {
+            const int d = d0 + 32 * u;
+            if (d >= K) break;
+            float z[H];
+            float mx = -INFINITY;
+#pragma unroll
+            for (int gg = 0; gg < G; gg++) {
+                z[4 * gg] = fmaf(c4[u][gg].x, kLog2e, ka[4 * gg]);
+                z[4 * gg + 1] = fmaf(c4[u][gg].y, kLog2e, ka[4 * gg + 1]);
+                z[4 * gg + 2] = fmaf(c4[u][gg].z, kLog2e, ka[4 * gg + 2]);
+                z[4 * gg + 3] = fmaf(c4[u][gg].w, kLog2e, ka[4 * gg + 3]);
+#pragma unroll
+                for (int k = 0; k < 4; k++) mx = fmaxf(mx, z[4 * gg + k]);
+            }
+            float v = -INFINITY;
+            if (mx > -INFINITY) {
+                float sacc = 0.f;
+#pragma unroll
+                for (int k = 0; k < H; k++) sacc += ex2(z[k] - mx);
+                v = (mx + lg2(sacc)) * kLn2;
+            }
+            out[d] = v;
+        }
+    }
+}
+
+// Backward, same layout of the work.  grad_content may alias content: a warp has finished reading its row
+// for the sums before it writes, and every element is read by the lane that overwrites it.
+template <int G>
+__global__ void __launch_bounds__(kLwWarps * 32)
+links_bwd_warp_kernel(const float *__restrict__ grad_links, const float *content, const float *__restrict__ log_gates,
+                      const float *__restrict__ links, const float *__restrict__ head_lse, LinksMask mk,
+                      float *grad_content, float *__restrict__ grad_log_gates, int B, int L, int K) {
+    constexpr int H = 4 * G;
+    constexpr int U = 4;   // vectors a lane has in flight
+    const int lane = threadIdx.x & 31;
+    const int64_t slot = (int64_t)blockIdx.x * kLwWarps + (threadIdx.x >> 5);
+    if (slot >= (int64_t)B * L) return;
+    const int64_t b = slot / L;
+    const int i = links_row_of_slot((int)(slot - b * L), L);
+    const int64_t row = b * L + i;
+    const int jhi = links_jhi(i, L, K, mk, row);
+    const int nj = jhi - i > 0 ? jhi - i : 0;
+    const unsigned char *np = mk.nonpad ? mk.nonpad + b * L + i + 1 : nullptr;
+    const float4 *src = reinterpret_cast<const float4 *>(content + (row * L + i + 1) * (int64_t)H);
+    float4 *dst = reinterpret_cast<float4 *>(grad_content + (row * L + i + 1) * (int64_t)H);
+    const float *gl = grad_links + row * (int64_t)K, *lk = links + row * (int64_t)K;
+    const int nvec = nj * G;
+    const int g = lane & (G - 1);
+    const float4 ninf = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    float lse2[4], kq[4];   // lse_h and (gate_h - lse_h), log2 units; -inf: the head takes no part
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const float lse = __ldg(head_lse + row * H + 4 * g + k);
+        lse2[k] = lse * kLog2e;
+        kq[k] = lse > -INFINITY ? (__ldg(log_gates + row * H + 4 * g + k) - lse) * kLog2e : -INFINITY;
+    }
+    // ---- pass 1: S_h = sum_j G[j] p[j,h],  p[j,h] = exp(c[j,h] - lse_h + gate_h - links[j])
+    float S[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int v0 = lane; v0 < nvec; v0 += 32 * U) {
+        float4 c4[U];
+        float l2[U], gd[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int v = v0 + 32 * u, d = v / G;
+            const bool live = v < nvec && !(np && !np[d]);
+            c4[u] = live ? __ldg(src + v) : ninf;
+            l2[u] = live ? __ldg(lk + d) * kLog2e : -INFINITY;
+            gd[u] = live ? __ldg(gl + d) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            if (!(l2[u] > -INFINITY)) continue;
+            const float c[4] = {c4[u].x, c4[u].y, c4[u].z, c4[u].w};
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                if (kq[k] > -INFINITY) S[k] += gd[u] * ex2(fmaf(c[k], kLog2e, kq[k]) - l2[u]);
+        }
+    }
+#pragma unroll
+    for (int o = G; o < 32; o <<= 1) {
+#pragma unroll
+        for (int k = 0; k < 4; k++) S[k] += __shfl_xor_sync(0xffffffffu, S[k], o);
+    }
+    if (lane < G) {
+#pragma unroll
+        for (int k = 0; k < 4; k++) grad_log_gates[row * H + 4 * g + k] = S[k];
+    }
+    // ---- pass 2: d/dc[j,h] = G[j] p[j,h] - exp(c[j,h] - lse_h) S_h; zeros in the rest of the dense row
+    for (int v0 = lane; v0 < nvec; v0 += 32 * U) {
+        float4 c4[U];
+        float l2[U], gd[U];
+        bool live[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int v = v0 + 32 * u, d = v / G;
+            live[u] = v < nvec && !(np && !np[d]);
+            c4[u] = live[u] ? src[v] : ninf;
+            l2[u] = live[u] ? __ldg(lk + d) * kLog2e : -INFINITY;
+            gd[u] = live[u] ? __ldg(gl + d) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int v = v0 + 32 * u;
+            if (v >= nvec) break;
+            float o[4] = {0.f, 0.f, 0.f, 0.f};
+            const float c[4] = {c4[u].x, c4[u].y, c4[u].z, c4[u].w};
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                if (c[k] > -INFINITY && kq[k] > -INFINITY) {
+                    const float soft = ex2(fmaf(c[k], kLog2e, -lse2[k]));
+                    const float pg = l2[u] > -INFINITY ? gd[u] * ex2(fmaf(c[k], kLog2e, kq[k]) - l2[u]) : 0.f;
+                    o[k] = pg - soft * S[k];
+                }
+            }
+            dst[v] = make_float4(o[0], o[1], o[2], o[3]);
+        }
+    }
+    // the rest of the row: successors up to and including i, and those past jhi
+    float4 *rowv = reinterpret_cast<float4 *>(grad_content + row * (int64_t)L * H);
+    const int head = (i + 1) * G, tail0 = (i + 1 + nj) * G, total = L * G;
+    for (int v = lane; v < head; v += 32) rowv[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int v = tail0 + lane; v < total; v += 32) rowv[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+static bool links_warp_form(int H, const void *a, const void *b) {
+    const int G = H / 4;
+    return H % 4 == 0 && (G == 1 || G == 2 || G == 4 || G == 8) &&
+           ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0;
+}
+
 static size_t links_smem_fwd(int L, int H) {
     return ((size_t)(L - 1) * H + 2 * kLinksThreads + 2 * H) * sizeof(float) + 16;
 }
@@ -230,6 +455,19 @@ int dat_links_from_heads(const float *content, const float *log_gates, const int
                 kLinksThreads);
     DeviceInfo di;
     if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
+    if (links_warp_form(heads, content, content)) {
+        const LinksMask mkw{bound_end, nonpad};
+        const int64_t rows = (int64_t)bsz * prelen;
+        const unsigned grid = (unsigned)((rows + kLwWarps - 1) / kLwWarps);
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        switch (heads / 4) {
+            case 1: links_fwd_warp_kernel<1><<<grid, kLwWarps * 32, 0, st>>>(content, log_gates, mkw, links, head_lse, bsz, prelen, translen); break;
+            case 2: links_fwd_warp_kernel<2><<<grid, kLwWarps * 32, 0, st>>>(content, log_gates, mkw, links, head_lse, bsz, prelen, translen); break;
+            case 4: links_fwd_warp_kernel<4><<<grid, kLwWarps * 32, 0, st>>>(content, log_gates, mkw, links, head_lse, bsz, prelen, translen); break;
+            default: links_fwd_warp_kernel<8><<<grid, kLwWarps * 32, 0, st>>>(content, log_gates, mkw, links, head_lse, bsz, prelen, translen); break;
+        }
+        return check_launch(who);
+    }
     const size_t smem = links_smem_fwd(prelen, heads);
     DAT_REQUIRE(smem <= (size_t)di.max_smem_optin, DAT_ERR_UNSUPPORTED,
                 "%s: prelen*heads = %d*%d needs %zu bytes of shared memory", who, prelen, heads, smem);
@@ -259,6 +497,21 @@ int dat_links_from_heads_backward(const float *grad_links, const float *content,
                 kLinksThreads);
     DeviceInfo di;
     if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
+    if (links_warp_form(heads, content, grad_content)) {
+        const LinksMask mkw{bound_end, nonpad};
+        const int64_t rows = (int64_t)bsz * prelen;
+        const unsigned grid = (unsigned)((rows + kLwWarps - 1) / kLwWarps);
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define DAT_LINKS_BWD(G_) links_bwd_warp_kernel<G_><<<grid, kLwWarps * 32, 0, st>>>(grad_links, content, log_gates, links, head_lse, mkw, grad_content, grad_log_gates, bsz, prelen, translen)
+        switch (heads / 4) {
+            case 1: DAT_LINKS_BWD(1); break;
+            case 2: DAT_LINKS_BWD(2); break;
+            case 4: DAT_LINKS_BWD(4); break;
+            default: DAT_LINKS_BWD(8); break;
+        }
+#undef DAT_LINKS_BWD
+        return check_launch(who);
+    }
     const size_t smem = links_smem_bwd(prelen, heads);
     DAT_REQUIRE(smem <= (size_t)di.max_smem_optin, DAT_ERR_UNSUPPORTED,
                 "%s: prelen*heads = %d*%d needs %zu bytes of shared memory", who, prelen, heads, smem);

@@ -178,7 +178,8 @@ def test_links_from_heads_matches_the_reference_fixture(name):
 
 
 @pytest.mark.parametrize("B,L,H,K,mask", [(3, 40, 8, 99999, "nonpad"), (2, 70, 16, 12, "nonpad"), (2, 33, 3, 99999, "bound"),
-                                          (2, 130, 8, 99999, None), (1, 20, 1, 5, "nonpad")])
+                                          (2, 130, 8, 99999, None), (1, 20, 1, 5, "nonpad"), (2, 48, 32, 20, "nonpad"),
+                                          (2, 45, 4, 99999, "bound")])
 def test_links_from_heads_matches_oracle(B, L, H, K, mask):
     gen = torch.Generator().manual_seed(L * H)
     content = torch.randn(B, L, L, H, generator=gen) * 2
