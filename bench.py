@@ -913,7 +913,7 @@ def extra_legs(torch, dev, ev, workloads, dag_loss, dag_best_alignment, dag_logs
 
     c3_flagged = flagged_counts(b, m, l)
     out["C3"] = {"workload": f"B={b.match_all.shape[0]}, L=1024, T={b.match_all.shape[1]}: alignment + dag_loss fwd+bwd "
-                             f"(rows do not fit in shared memory: tiled sweep with row-wide scaling)",
+                             f"(rows do not fit in one SM's shared memory: sweep by clusters of 16 CTAs)",
                  "ms_per_step": med, "ms_min": lo, "ms_max": hi,
                  "sentences_per_s": b.match_all.shape[0] / (med * 1e-3),
                  "flagged_sentences": c3_flagged[0], "exact_backward_only_sentences": c3_flagged[1]}

@@ -43,6 +43,11 @@ constexpr float kMaxSpread = 100.f;        // row-wide spread (bits) a sentence 
 constexpr float kMaxSpreadLocal = 140.f;   // spread inside a 32-vertex sub-strip (the flush there is 2^-190 relative)
 constexpr float kMaxSpreadBackward = 200.f;   // row-wide spread up to which grad_links may use the product form
 constexpr float kMinLog2Input = -120.f;  // finite links / matches below this go to the exact kernel
+// The tiled sweep scales a whole row by one power of two, and the row-wide spread it may have (kMaxSpread)
+// is used up by the length of the target alone: on diffuse graphs the spread grows by about 0.75 bits per
+// target step (132 steps: 96 bits, 255 steps: 190-200 bits; peaky graphs need more), so a sentence with more
+// steps than this is not swept at all but handed to the exact kernels up front, which would redo it anyway.
+constexpr int kTiledMaxSteps = 128;
 // Per-sentence word in the scratch.  The sweeps OR in what they saw; dag_fast_check_kernel turns it
 // into the verdict the later launches read.
 constexpr int kFlagTiny = 1;            // in: a finite link or in-window match below 2^kMinLog2Input
@@ -115,7 +120,7 @@ dag_fast_prep_kernel(const float *__restrict__ links, const int64_t *__restrict_
     const int lane = threadIdx.x & 31;
     if (i >= rows) return;
     const long long oll = output_length[b], tll = target_length[b];
-    if (!lengths_valid(oll, tll, T, L)) return;  // the sweep never reads this sentence
+    if (!lengths_valid(oll, tll, T, L) || tll > kTiledMaxSteps) return;  // the sweep never reads this sentence
     const int ol = (int)oll;
     const float *brow = links + ((size_t)b * L + (i < L ? i : 0)) * K;
     float4 *erow = reinterpret_cast<float4 *>(esq_all + ((size_t)b * rows + i) * pitch);
@@ -236,6 +241,10 @@ dag_fast_sweep_kernel(const float *__restrict__ match_all, const float *__restri
         return;
     }
     const int ol = (int)oll, tl = (int)tll;
+    if (tl > kTiledMaxSteps) {   // its row-wide spread would not pass the check: straight to the exact kernels
+        if (tid == 0) atomicOr(flag + b, kFlagTiny);
+        return;
+    }
     const int W = ol - tl + 1;
     const int rp = pitch + 32;                // row buffers carry 32 floats of zero padding
     float *abuf0 = fsm, *abuf1 = fsm + rp, *bbuf0 = fsm + 2 * rp, *bbuf1 = fsm + 3 * rp;
@@ -538,6 +547,7 @@ dag_fast_check_kernel(const double *__restrict__ offsets_all, const float *__res
 }
 
 }  // namespace dat
+#include "dag_cluster.cuh"
 #include "dag_grad_umma.cuh"
 namespace dat {
 
@@ -697,7 +707,49 @@ int dat_dag_loss_fast(const float *match_all, const float *links, const int64_t 
     const int *order = do_order ? sc.order : nullptr;
     const int strip_rp = strip_row_pitch(prelen);
     const size_t strip_smem = strip_smem_floats(tarlen, strip_rp) * sizeof(float);
-    if (strip_applicable(tarlen, prelen, di)) {
+    // Rows that do not fit in shared memory: a cluster of 4, 8 or 16 CTAs per direction, if the sentence's blocks
+    // of exp(links) fit its registers and the device can co-schedule such a cluster
+    int cl_ranks = 0;
+    cudaLaunchConfig_t ccfg = {};
+    cudaLaunchAttribute cattr[1];
+    const size_t csmem = cluster_smem_bytes(prelen);
+    if (!strip_applicable(tarlen, prelen, di)) {
+        for (int r = 4; r <= kClMaxRanks && !cl_ranks; r *= 2)
+            if (cluster_fits(prelen, r)) cl_ranks = r;
+        if (cl_ranks) {
+            bool ok = csmem <= (size_t)di.max_smem_optin;
+            if (ok && csmem > 48 * 1024)
+                ok = cudaFuncSetAttribute(dag_cluster_sweep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)csmem) == cudaSuccess;
+            if (ok && cl_ranks > 8)
+                ok = cudaFuncSetAttribute(dag_cluster_sweep_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) ==
+                     cudaSuccess;
+            ccfg.gridDim = dim3(2u * (unsigned)bsz * (unsigned)cl_ranks);
+            ccfg.blockDim = dim3(kClThreads);
+            ccfg.dynamicSmemBytes = csmem;
+            ccfg.stream = st;
+            cattr[0].id = cudaLaunchAttributeClusterDimension;
+            cattr[0].val.clusterDim.x = (unsigned)cl_ranks;
+            cattr[0].val.clusterDim.y = 1;
+            cattr[0].val.clusterDim.z = 1;
+            ccfg.attrs = cattr;
+            ccfg.numAttrs = 1;
+            int nclusters = 0;
+            if (ok) ok = cudaOccupancyMaxActiveClusters(&nclusters, dag_cluster_sweep_kernel, &ccfg) == cudaSuccess &&
+                         nclusters >= 1;
+            if (!ok) {
+                cudaGetLastError();   // not an error of the call: the tiled sweep takes over
+                cl_ranks = 0;
+            }
+        }
+    }
+    if (cl_ranks) {
+        if (cudaLaunchKernelEx(&ccfg, dag_cluster_sweep_kernel, match_all, links, output_length, target_length, order,
+                               alpha, beta, offsets, sc.chk, sc.sub, sc.flag, loss, status, tarlen, prelen, translen,
+                               fast_sub_strips(prelen)) != cudaSuccess)
+            return check_launch("dat_dag_loss_fast(cluster sweep)");
+        if (int rc = check_launch("dat_dag_loss_fast(cluster sweep)")) return rc;
+    } else if (strip_applicable(tarlen, prelen, di)) {
         // all rows of a sentence fit in shared memory: strip-ordered sweep, one CTA per direction
         if (cudaFuncSetAttribute(dag_strip_sweep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)strip_smem) != cudaSuccess)
@@ -726,7 +778,8 @@ int dat_dag_loss_fast(const float *match_all, const float *links, const int64_t 
         if (int rc = check_launch("dat_dag_loss_fast(sweep)")) return rc;
     }
     if (!strip_applicable(tarlen, prelen, di)) {   // (the strip sweep's CTAs run the check themselves)
-        dag_fast_check_kernel<<<(unsigned)bsz, kCheckThreads, 0, st>>>(offsets, sc.chk, nullptr, fast_sub_strips(prelen),
+        dag_fast_check_kernel<<<(unsigned)bsz, kCheckThreads, 0, st>>>(offsets, sc.chk, cl_ranks ? sc.sub : nullptr,
+                                                                       fast_sub_strips(prelen),
                                                                        output_length, target_length, sc.flag, status, bsz,
                                                                        tarlen, prelen);
         if (int rc = check_launch("dat_dag_loss_fast(check)")) return rc;

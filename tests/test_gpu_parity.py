@@ -61,6 +61,9 @@ def check_dag_against_oracle(batch, grad_out=None):
     (9, 2, 190, 100, None), (10, 2, 190, 100, 40),
     # graphs longer than 1024 vertices (a thread of the exact alpha sweep then finalises more than two columns)
     (11, 2, 1300, 12, None), (12, 1, 2048, 6, 700),
+    # rows that do not fit in one SM's shared memory: the sweep by a cluster of 8 / 16 CTAs (and, longer than
+    # 1024 vertices with many steps, the tiled sweep or the exact kernels)
+    (13, 2, 700, 120, None), (14, 2, 1000, 150, 300), (15, 1, 1024, 70, None), (16, 2, 1100, 140, None),
 ])
 def test_dag_loss_matches_oracle(seed, B, L, T, K):
     batch = workloads.small_batch(seed=seed, B=B, L=L, T=T, V=50, translen=K)
