@@ -239,8 +239,7 @@ dag_cluster_sweep_kernel(const float *__restrict__ match_all, const float *__res
             asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 1;" ::: "memory");
         }
         // the row offset of step s: the largest exponent of the previous row (the same in every CTA)
-        int offe = kExpNone;
-        for (int c = 0; c < nsub; c++) offe = exc[c] > offe ? exc[c] : offe;
+        const int offe = __reduce_max_sync(0xffffffffu, lane < nsub ? exc[lane] : kExpNone);
         // what the finished step left behind for the check: row maxima over the sub-strips (one step late)
         if (rank == 0 && warp == kClWarps - 1) {
             const int sp = s - 1, tp = rev ? tl - 1 - sp : sp;
@@ -278,19 +277,29 @@ dag_cluster_sweep_kernel(const float *__restrict__ match_all, const float *__res
         if (warp < nd) {
             const int d = sm.dlist[warp], base = sm.dbase[warp], u = 32 * d + lane;
             const bool reach = 32 * d + 31 >= s && 32 * d <= s + W - 1;
-            int est = kExpNone;
-            for (int c = 0; c <= d; c++) {
-                const int mg = sm.slotmag[base + c];
-                est = mg > est ? mg : est;
-            }
+            // lane c looks at slot c (a sentence has at most 32 sub-strips): the largest magnitude decides the unit,
+            // and every slot's scale 2^(exponent of its source - unit) is prepared as two exact factors
+            // (scale2's rule) by its lane and handed round by shuffles
+            const int mg = lane <= d ? sm.slotmag[base + lane] : kExpNone;
+            const int est = __reduce_max_sync(0xffffffffu, mg);
             float y = 0.f, val = 0.f;
             int U = kExpNone;
             const bool inside = u >= s && u <= s + W - 1 && u < ol;
             if (est != kExpNone && reach) {
                 U = est - kTargetExp;
+                float f1 = 0.f, f2 = 0.f;
+                if (mg != kExpNone) {
+                    int k = exc[lane] - U;
+                    if (k >= -252) {
+                        k = k > 254 ? 254 : k;
+                        const int k1 = (k >= -126 && k <= 127) ? k : k / 2;
+                        f1 = __int_as_float((k1 + 127) << 23);
+                        f2 = __int_as_float((k - k1 + 127) << 23);
+                    }
+                }
                 for (int c = 0; c <= d; c++) {
-                    if (sm.slotmag[base + c] == kExpNone) continue;
-                    val += scale2(sm.slot[(base + c) * 32 + lane], exc[c] - U);
+                    const float g1 = __shfl_sync(0xffffffffu, f1, c), g2 = __shfl_sync(0xffffffffu, f2, c);
+                    val += (sm.slot[(base + c) * 32 + lane] * g1) * g2;
                 }
                 const float m2 = sm.M[((s & (kClMRing - 1)) * kClMaxDest + warp) * 32 + lane] * kLog2e;
                 ir.fin = fminf(ir.fin, (inside && m2 > -INFINITY) ? m2 : INFINITY);
@@ -311,13 +320,14 @@ dag_cluster_sweep_kernel(const float *__restrict__ match_all, const float *__res
             const float hv = (vb != 0u && U != kExpNone) ? lg2(__uint_as_float(vb)) + (float)U : -INFINITY;
             // next row, exponent and maxima into every CTA of the cluster
             float *rown = sm.row + nxt * Lp + u;
+            // (lanes 0, 1, 2 carry the block's exponent and its two maxima: one store per CTA for the three)
+            const void *meta = lane == 0 ? (const void *)(sm.ex + nxt * kClMaxSub + d)
+                             : lane == 1 ? (const void *)(sm.mx + (nxt * 2 + 0) * kClMaxSub + d)
+                                         : (const void *)(sm.mx + (nxt * 2 + 1) * kClMaxSub + d);
+            const int metav = lane == 0 ? e : lane == 1 ? __float_as_int(hy) : __float_as_int(hv);
             for (int r = 0; r < nranks; r++) {
                 cluster_st_f32(cluster_map(rown, r), y);
-                if (lane == 0) {
-                    cluster_st_s32(cluster_map(sm.ex + nxt * kClMaxSub + d, r), e);
-                    cluster_st_f32(cluster_map(sm.mx + (nxt * 2 + 0) * kClMaxSub + d, r), hy);
-                    cluster_st_f32(cluster_map(sm.mx + (nxt * 2 + 1) * kClMaxSub + d, r), hv);
-                }
+                if (lane < 3) cluster_st_s32(cluster_map(meta, r), metav);
             }
             // the output row: log2 values relative to the row offset
             o_off = offe != kExpNone ? offe : 0;
