@@ -518,6 +518,12 @@ dag_align_strip_kernel(const float *__restrict__ match_all, const float *__restr
     }
 }
 
+}  // namespace dat
+
+#include "dag_align_cluster.cuh"
+
+namespace dat {
+
 static inline size_t align_smem_bytes(int L, int nrows) {
     const int pitch = align_pitch(L);
     return ((size_t)pitch * 4 + (size_t)nrows * (pitch + 32) * 4 + 15) & ~(size_t)15;
@@ -572,6 +578,45 @@ int dat_dag_best_alignment(const float *match_all, const float *links,
                 match_all, links, output_length, target_length, path, max_score, status, tarlen, prelen,
                 translen, lg, rp);
             return check_launch("dat_dag_best_alignment");
+        }
+    }
+    {
+        // rows that do not fit one SM: a cluster of 4, 8 or 16 CTAs per sentence, if the sentence's blocks of links
+        // fit its registers and the device can co-schedule such a cluster
+        int cl_ranks = 0;
+        for (int r = 4; r <= kClMaxRanks && !cl_ranks; r *= 2)
+            if (cluster_fits(prelen, r)) cl_ranks = r;
+        const size_t csmem = align_cluster_smem_bytes(prelen);
+        if (cl_ranks && csmem <= (size_t)di.max_smem_optin) {
+            bool ok = true;
+            if (csmem > 48 * 1024)
+                ok = cudaFuncSetAttribute(dag_align_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)csmem) == cudaSuccess;
+            if (ok && cl_ranks > 8)
+                ok = cudaFuncSetAttribute(dag_align_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) ==
+                     cudaSuccess;
+            cudaLaunchConfig_t ccfg = {};
+            cudaLaunchAttribute cattr[1];
+            ccfg.gridDim = dim3((unsigned)bsz * (unsigned)cl_ranks);
+            ccfg.blockDim = dim3(kClThreads);
+            ccfg.dynamicSmemBytes = csmem;
+            ccfg.stream = st;
+            cattr[0].id = cudaLaunchAttributeClusterDimension;
+            cattr[0].val.clusterDim.x = (unsigned)cl_ranks;
+            cattr[0].val.clusterDim.y = 1;
+            cattr[0].val.clusterDim.z = 1;
+            ccfg.attrs = cattr;
+            ccfg.numAttrs = 1;
+            int nclusters = 0;
+            if (ok) ok = cudaOccupancyMaxActiveClusters(&nclusters, dag_align_cluster_kernel, &ccfg) == cudaSuccess &&
+                         nclusters >= 1;
+            if (ok) {
+                if (cudaLaunchKernelEx(&ccfg, dag_align_cluster_kernel, match_all, links, output_length, target_length,
+                                       path, max_score, rows_ws, status, tarlen, prelen, translen, lg) != cudaSuccess)
+                    return check_launch("dat_dag_best_alignment(cluster)");
+                return check_launch("dat_dag_best_alignment(cluster)");
+            }
+            cudaGetLastError();   // not an error of the call: the tiled kernel takes over
         }
     }
     {

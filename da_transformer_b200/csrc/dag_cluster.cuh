@@ -28,37 +28,9 @@
 // tiled sweep with its row-wide scaling (which such sentences fail) and then the exact kernels.
 #pragma once
 
+#include "cluster_util.cuh"
+
 namespace dat {
-
-constexpr int kClMaxRanks = 16;      // CTAs per cluster: 4, 8 or 16 (the smallest whose registers hold the sentence's blocks)
-constexpr int kClThreads = 512;
-constexpr int kClWarps = kClThreads / 32;
-constexpr int kClPerWarp = 3;        // blocks of E a warp can hold
-constexpr int kClMaxBlocks = kClWarps * kClPerWarp;   // per CTA
-constexpr int kClMaxDest = 8;        // destination blocks a CTA can own
-constexpr int kClMaxSub = 32;        // sub-strips a sentence can have here (bounded by the block capacity)
-constexpr int kClMRing = 8;          // steps of match values staged ahead
-
-// blocks of the pairs dealt to `rank`: destination blocks d = p and nsub-1-p for p = rank, rank + nranks, ...
-__host__ __device__ inline int cluster_blocks_of_rank(int nsub, int rank, int nranks) {
-    int n = 0;
-    for (int p = rank; 2 * p < nsub; p += nranks) {
-        n += p + 1;
-        if (nsub - 1 - p != p) n += nsub - p;
-    }
-    return n;
-}
-__host__ __device__ inline bool cluster_fits(int prelen, int nranks) {
-    const int nsub = (prelen + 31) / 32;
-    if (nsub > kClMaxSub) return false;
-    for (int r = 0; r < nranks; r++) {
-        if (cluster_blocks_of_rank(nsub, r, nranks) > kClMaxBlocks) return false;
-        int nd = 0;
-        for (int p = r; 2 * p < nsub; p += nranks) nd += (nsub - 1 - p != p) ? 2 : 1;
-        if (nd > kClMaxDest) return false;
-    }
-    return true;
-}
 
 struct ClusterSmem {
     float *row;      // [2][Lp]      mantissas of the previous / next row (every CTA holds the whole row)
@@ -74,24 +46,6 @@ __host__ __device__ inline size_t cluster_smem_bytes(int prelen) {
     const int Lp = ((prelen + 31) / 32) * 32;
     return (size_t)(2 * Lp + 2 * kClMaxSub + 4 * kClMaxSub + kClMaxBlocks * 32 + kClMaxBlocks +
                     kClMRing * kClMaxDest * 32 + 2 * kClMaxBlocks + 2 * kClMaxDest) * sizeof(float) + 64;
-}
-
-__device__ __forceinline__ uint32_t cluster_map(const void *p, int rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"((uint32_t)__cvta_generic_to_shared(p)), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void cluster_st_f32(uint32_t addr, float v) {
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
-__device__ __forceinline__ void cluster_st_s32(uint32_t addr, int v) {
-    asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
-}
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-__device__ __forceinline__ void cluster_barrier() {
-    cluster_arrive();
-    cluster_wait();
 }
 
 __global__ void __launch_bounds__(kClThreads, 1)

@@ -106,6 +106,9 @@ def test_forced_alignment_match_with_minus_inf_and_zero():
     (1, 5, 24, 6, None, 0), (2, 4, 40, 9, 6, 0), (3, 4, 70, 12, None, 0.5), (4, 3, 97, 13, 20, 1.0),
     (5, 2, 160, 20, None, 0.25), (6, 2, 64, 5, None, 2.0), (7, 2, 190, 100, None, 0.5), (8, 2, 190, 100, 40, 0.5),
     (9, 1, 1300, 12, None, 0.5),
+    # rows that do not fit one SM's shared memory: clusters of 16, 8 and 4 CTAs per sentence
+    (10, 2, 1000, 150, None, 0.5), (11, 2, 700, 120, 300, 0.25), (12, 2, 400, 200, None, 1.0),
+    (13, 1, 1024, 70, None, 0.0),
 ])
 def test_best_alignment_bit_exact(config, seed, B, L, T, K, quant):
     batch = workloads.small_batch(seed=seed, B=B, L=L, T=T, V=50, translen=K)
