@@ -324,6 +324,15 @@ __device__ __forceinline__ void strip_load_block(float (&e)[32], const float *__
     }
 }
 
+// (x, y) = (a0 + b0, a1 + b1), each rounded to nearest like __fadd_rn: the two-lane fp32 add of sm_100, one
+// issue slot for two additions (these kernels are bound by issue slots, not by the adders)
+__device__ __forceinline__ void fadd2_rn(float &x, float &y, float a0, float a1, float b0, float b1) {
+    asm("{\n\t.reg .b64 ra, rb, rc;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "add.rn.f32x2 rc, ra, rb;\n\tmov.b64 {%0, %1}, rc;\n\t}"
+        : "=f"(x), "=f"(y)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+
 // max over the 32 rows of a block of arow[r] + e[r]; arow is read as broadcast 16-byte loads
 __device__ __forceinline__ float strip_block_max(const float *arow, const float (&e)[32]) {
     float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
@@ -331,10 +340,15 @@ __device__ __forceinline__ float strip_block_max(const float *arow, const float 
     for (int q = 0; q < 8; q += 2) {
         const float4 a = *reinterpret_cast<const float4 *>(arow + 4 * q);
         const float4 b = *reinterpret_cast<const float4 *>(arow + 4 * q + 4);
-        m0 = max3(m0, __fadd_rn(a.x, e[4 * q]), __fadd_rn(a.y, e[4 * q + 1]));
-        m1 = max3(m1, __fadd_rn(a.z, e[4 * q + 2]), __fadd_rn(a.w, e[4 * q + 3]));
-        m2 = max3(m2, __fadd_rn(b.x, e[4 * q + 4]), __fadd_rn(b.y, e[4 * q + 5]));
-        m3 = max3(m3, __fadd_rn(b.z, e[4 * q + 6]), __fadd_rn(b.w, e[4 * q + 7]));
+        float s0, s1, s2, s3, s4, s5, s6, s7;
+        fadd2_rn(s0, s1, a.x, a.y, e[4 * q], e[4 * q + 1]);
+        fadd2_rn(s2, s3, a.z, a.w, e[4 * q + 2], e[4 * q + 3]);
+        fadd2_rn(s4, s5, b.x, b.y, e[4 * q + 4], e[4 * q + 5]);
+        fadd2_rn(s6, s7, b.z, b.w, e[4 * q + 6], e[4 * q + 7]);
+        m0 = max3(m0, s0, s1);
+        m1 = max3(m1, s2, s3);
+        m2 = max3(m2, s4, s5);
+        m3 = max3(m3, s6, s7);
     }
     return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
@@ -346,17 +360,23 @@ __device__ __forceinline__ void strip_block_max2(const float *arow, const float 
 #pragma unroll
     for (int q = 0; q < 8; q++) {
         const float4 a = *reinterpret_cast<const float4 *>(arow + 4 * q);
-        m0 = max3(m0, __fadd_rn(a.x, e0[4 * q]), __fadd_rn(a.y, e0[4 * q + 1]));
-        m1 = max3(m1, __fadd_rn(a.z, e0[4 * q + 2]), __fadd_rn(a.w, e0[4 * q + 3]));
-        n0 = max3(n0, __fadd_rn(a.x, e1[4 * q]), __fadd_rn(a.y, e1[4 * q + 1]));
-        n1 = max3(n1, __fadd_rn(a.z, e1[4 * q + 2]), __fadd_rn(a.w, e1[4 * q + 3]));
+        float s0, s1, s2, s3, u0, u1, u2, u3;
+        fadd2_rn(s0, s1, a.x, a.y, e0[4 * q], e0[4 * q + 1]);
+        fadd2_rn(s2, s3, a.z, a.w, e0[4 * q + 2], e0[4 * q + 3]);
+        fadd2_rn(u0, u1, a.x, a.y, e1[4 * q], e1[4 * q + 1]);
+        fadd2_rn(u2, u3, a.z, a.w, e1[4 * q + 2], e1[4 * q + 3]);
+        m0 = max3(m0, s0, s1);
+        m1 = max3(m1, s2, s3);
+        n0 = max3(n0, u0, u1);
+        n1 = max3(n1, u2, u3);
     }
     r0 = fmaxf(m0, m1);
     r1 = fmaxf(n0, n1);
 }
 
-// Items (32-row block c, step t) of strip S for c in [c_first, c_last]; bulk warp wb takes a
+// Items (32-row block c, step t) of strip S for c in [c_first, c_last]; bulk warp wb of kBulkWarps takes a
 // contiguous share and merges its maxima into Pbuf[t][0..63].
+template <int kBulkWarps>
 __device__ __forceinline__ void strip_bulk(const float *__restrict__ links, const float *A, unsigned *Pbuf,
                                            int c_first, int c_last, int S, int wb, int lane, int K,
                                            int ol, int tl, int W, int rp) {
@@ -368,7 +388,7 @@ __device__ __forceinline__ void strip_bulk(const float *__restrict__ links, cons
         int tb = 32 * c + 32; tb = tb < t1 ? tb : t1;
         total += tb >= ta ? tb - ta + 1 : 0;
     }
-    const int lo = (wb * total) / kStripBulkWarps, hi = ((wb + 1) * total) / kStripBulkWarps;
+    const int lo = (wb * total) / kBulkWarps, hi = ((wb + 1) * total) / kBulkWarps;
     int base = 0;
     for (int c = c_first; c <= c_last; c++) {
         int ta = 32 * c - W + 2; ta = ta > t0 ? ta : t0;
@@ -392,43 +412,29 @@ __device__ __forceinline__ void strip_bulk(const float *__restrict__ links, cons
     }
 }
 
-__global__ void __launch_bounds__(kAlignThreads, 1)
-dag_align_strip_kernel(const float *__restrict__ match_all, const float *__restrict__ links_all,
-                       const int64_t *__restrict__ output_length, const int64_t *__restrict__ target_length,
-                       int64_t *__restrict__ path_out, float *__restrict__ max_score,
-                       int32_t *__restrict__ status, int T, int L, int K, int lg, int rp) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    __shared__ unsigned long long bt_key[2][kAlignWarps];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int b = blockIdx.x;
-    int64_t *path = path_out + (size_t)b * L;
-    for (int j = tid; j < L; j += kAlignThreads) path[j] = -1;
-    const long long oll = output_length[b], tll = target_length[b];
-    if (!lengths_valid(oll, tll, T, L)) {
-        if (tid == 0) {
-            if (max_score) max_score[b] = -INFINITY;
-            if (status) atomicOr(status, DAT_STATUS_BAD_LENGTH);
-        }
-        return;
-    }
-    const int ol = (int)oll, tl = (int)tll;
-    const int W = ol - tl + 1;
-    const float *match = match_all + (size_t)b * T * L;
-    const float *links = links_all + (size_t)b * L * K;
-    float *A = reinterpret_cast<float *>(smem_raw);                    // [T][rp] rows, absolute columns
-    unsigned *P = reinterpret_cast<unsigned *>(A + (size_t)T * rp);    // [2][T][64] merged maxima of a strip
-    float *M = reinterpret_cast<float *>(P + 2 * T * 64);              // [2][T][64] match values of a strip
-    const unsigned key_none = orderable(-INFINITY);
+// barrier among the first kWarps warps of the CTA (all of them: the sweep's warps)
+template <int kWarps>
+__device__ __forceinline__ void sweep_sync() {
+    asm volatile("bar.sync 2, %0;" ::"n"(kWarps * 32) : "memory");
+}
 
-    for (int x = tid; x < tl * rp; x += kAlignThreads) A[x] = -INFINITY;
-    for (int x = tid; x < 2 * T * 64; x += kAlignThreads) P[x] = key_none;
-    for (int x = tid; x < tl * 64; x += kAlignThreads) {
+// The strip-ordered sweep of one sentence by warps 0 .. kWarps-1 of the CTA (3 diagonal warps, the others
+// bulk): fills A[t][j] (absolute columns, -inf outside the window) for every step.
+template <int kWarps>
+__device__ __forceinline__ void align_strip_sweep(const float *__restrict__ match, const float *__restrict__ links,
+                                                  float *A, unsigned *P, float *M, int ol, int tl, int W, int T,
+                                                  int L, int K, int rp, int tid, int lane, int warp) {
+    constexpr int kThreads = kWarps * 32, kBulk = kWarps - kStripDiagWarps;
+    const unsigned key_none = orderable(-INFINITY);
+    for (int x = tid; x < tl * rp; x += kThreads) A[x] = -INFINITY;
+    for (int x = tid; x < 2 * T * 64; x += kThreads) P[x] = key_none;
+    for (int x = tid; x < tl * 64; x += kThreads) {
         const int t = x >> 6, jj = x & 63;
         M[x] = jj < L ? match[(size_t)t * L + jj] : 0.f;
     }
-    __syncthreads();
+    sweep_sync<kWarps>();
     if (tid == 0) A[0] = match[0];
-    __syncthreads();
+    sweep_sync<kWarps>();
 
     const int nS = (ol + 63) >> 6;
     for (int S = 0; S < nS; S++) {
@@ -436,14 +442,14 @@ dag_align_strip_kernel(const float *__restrict__ match_all, const float *__restr
         const float *Mcur = M + (S & 1) * T * 64;
         float *Mnext = M + ((S + 1) & 1) * T * 64;
         // ---- stage A: the items of strip S whose rows are strip S-1 (finished just now)
-        for (int x = tid; x < tl * 64; x += kAlignThreads) Pnext[x] = key_none;
+        for (int x = tid; x < tl * 64; x += kThreads) Pnext[x] = key_none;
         float ed[32];   // diagonal warps: their block, in flight across the barrier
         if (warp == 0) strip_load_block(ed, links, 2 * S, 2 * S, lane, K, ol);
         else if (warp == 1) strip_load_block(ed, links, 2 * S + 1, 2 * S + 1, lane, K, ol);
         else if (warp == 2) strip_load_block(ed, links, 2 * S, 2 * S + 1, lane, K, ol);
         else if (S >= 1)
-            strip_bulk(links, A, Pcur, 2 * S - 2, 2 * S - 1, S, warp - kStripDiagWarps, lane, K, ol, tl, W, rp);
-        __syncthreads();
+            strip_bulk<kBulk>(links, A, Pcur, 2 * S - 2, 2 * S - 1, S, warp - kStripDiagWarps, lane, K, ol, tl, W, rp);
+        sweep_sync<kWarps>();
         // ---- stage B: warps 0-2 walk the diagonal blocks of strip S; the others work ahead on strip S+1
         if (warp < kStripDiagWarps) {
             int t0 = 64 * S - W + 1; t0 = t0 > 1 ? t0 : 1;
@@ -473,7 +479,7 @@ dag_align_strip_kernel(const float *__restrict__ match_all, const float *__restr
                 diag_group_sync();
             }
         } else if (S + 1 < nS) {
-            for (int x = tid - 32 * kStripDiagWarps; x < tl * 64; x += kAlignThreads - 32 * kStripDiagWarps) {
+            for (int x = tid - 32 * kStripDiagWarps; x < tl * 64; x += kThreads - 32 * kStripDiagWarps) {
                 const int t = x >> 6, jj = 64 * (S + 1) + (x & 63);
                 if (jj < L) cp_async4(Mnext + x, match + (size_t)t * L + jj);
                 else Mnext[x] = 0.f;
@@ -481,12 +487,42 @@ dag_align_strip_kernel(const float *__restrict__ match_all, const float *__restr
             if (S >= 1) {
                 int cmin = 2 * S + 1 - (K - 1) / 32;   // blocks further left hold no transition into strip S+1
                 cmin = cmin > 0 ? cmin : 0;
-                strip_bulk(links, A, Pnext, cmin, 2 * S - 1, S + 1, warp - kStripDiagWarps, lane, K, ol, tl, W, rp);
+                strip_bulk<kBulk>(links, A, Pnext, cmin, 2 * S - 1, S + 1, warp - kStripDiagWarps, lane, K, ol, tl, W, rp);
             }
             cp_async_wait_all();
         }
-        __syncthreads();
+        sweep_sync<kWarps>();
     }
+}
+
+// One CTA per sentence: the sweep by all 16 warps, then the backtrace by all of them.
+__global__ void __launch_bounds__(kAlignThreads, 1)
+dag_align_strip_kernel(const float *__restrict__ match_all, const float *__restrict__ links_all,
+                       const int64_t *__restrict__ output_length, const int64_t *__restrict__ target_length,
+                       int64_t *__restrict__ path_out, float *__restrict__ max_score,
+                       int32_t *__restrict__ status, int T, int L, int K, int lg, int rp) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ unsigned long long bt_key[2][kAlignWarps];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int b = blockIdx.x;
+    int64_t *path = path_out + (size_t)b * L;
+    for (int j = tid; j < L; j += kAlignThreads) path[j] = -1;
+    const long long oll = output_length[b], tll = target_length[b];
+    if (!lengths_valid(oll, tll, T, L)) {
+        if (tid == 0) {
+            if (max_score) max_score[b] = -INFINITY;
+            if (status) atomicOr(status, DAT_STATUS_BAD_LENGTH);
+        }
+        return;
+    }
+    const int ol = (int)oll, tl = (int)tll;
+    const int W = ol - tl + 1;
+    const float *match = match_all + (size_t)b * T * L;
+    const float *links = links_all + (size_t)b * L * K;
+    float *A = reinterpret_cast<float *>(smem_raw);                    // [T][rp] rows, absolute columns
+    unsigned *P = reinterpret_cast<unsigned *>(A + (size_t)T * rp);    // [2][T][64] merged maxima of a strip
+    float *M = reinterpret_cast<float *>(P + 2 * T * 64);              // [2][T][64] match values of a strip
+    align_strip_sweep<kAlignWarps>(match, links, A, P, M, ol, tl, W, T, L, K, rp, tid, lane, warp);
 
     // backtrace (dag_best_alignment.cu:185-188).  At each step every thread re-evaluates one
     // candidate predecessor of the path vertex; the CTA keeps the largest (value, rank) key.
@@ -518,6 +554,172 @@ dag_align_strip_kernel(const float *__restrict__ match_all, const float *__restr
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Persistent form of the strip kernel for batches of more sentences than SMs.  The backtrace of a
+// sentence is one chain of tl-1 dependent round trips to the links in L2 (the column of the path vertex is
+// known only when the previous step is resolved) during which the SM does nothing else, about a fifth of
+// the sentence's time.  Here a CTA stays on its SM and takes sentences from a counter, most expensive
+// first; warps 0-14 sweep a sentence, copy its rows to the caller's workspace and go on to the next
+// sentence, while warp 15 runs the backtrace of the one before from the workspace.  The two sides meet
+// at two named barriers (rows handed over / backtrace finished), so the sweep is at most one sentence
+// ahead; nothing spins.
+// ---------------------------------------------------------------------------------------------
+constexpr int kPersSweepWarps = kAlignWarps - 1;       // (a seventeenth warp would cap the registers at 96 per thread:
+constexpr int kPersSweepThreads = 32 * kPersSweepWarps; //  five warps on one scheduler; the bulk warps need 128)
+constexpr int kPersThreads = kPersSweepThreads + 32;   // + the backtrace warp
+
+__device__ __forceinline__ void pers_bar_sync(int id) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(kPersThreads) : "memory");
+}
+__device__ __forceinline__ void pers_bar_arrive(int id) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "n"(kPersThreads) : "memory");
+}
+constexpr int kBarHandOver = 3, kBarBacktraced = 4;
+
+// Sentences ranked by decreasing cost (tl-1) * W^2 and the work counter set to zero.  One CTA.
+__global__ void __launch_bounds__(1024)
+dag_align_order_kernel(const int64_t *__restrict__ output_length, const int64_t *__restrict__ target_length,
+                       int *__restrict__ order, int *__restrict__ counter, int B, int T, int L) {
+    extern __shared__ float align_cost_s[];
+    if (threadIdx.x == 0) *counter = 0;
+    for (int b = threadIdx.x; b < B; b += blockDim.x) {
+        const long long ol = output_length[b], tl = target_length[b];
+        float c = 0.f;
+        if (lengths_valid(ol, tl, T, L)) {
+            const float W = (float)(ol - tl + 1);
+            c = (float)(tl - 1) * W * W;
+        }
+        align_cost_s[b] = c;
+    }
+    __syncthreads();
+    for (int b = threadIdx.x; b < B; b += blockDim.x) {
+        const float c = align_cost_s[b];
+        int rank = 0;
+        for (int o = 0; o < B; o++) {
+            const float co = align_cost_s[o];
+            rank += (co > c) || (co == c && o < b);
+        }
+        order[rank] = b;
+    }
+}
+
+__global__ void __launch_bounds__(kPersThreads, 1)
+dag_align_strip_persistent_kernel(const float *__restrict__ match_all, const float *__restrict__ links_all,
+                                  const int64_t *__restrict__ output_length,
+                                  const int64_t *__restrict__ target_length, const int *__restrict__ order,
+                                  int *__restrict__ counter, int64_t *__restrict__ path_out,
+                                  float *__restrict__ max_score, float *rows_ws, int32_t *__restrict__ status,
+                                  int B, int T, int L, int K, int lg, int rp) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int mail[4];       // sentence handed to the backtrace warp (-1: no more), its lengths
+    __shared__ int fetched[2];    // the counter's value, alternating slots
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    if (warp == kPersSweepWarps) {
+        // ---- the backtrace warp (dag_best_alignment.cu:185-188): each lane re-evaluates its share of the candidate
+        // predecessors of the path vertex; the warp keeps the largest (value, rank) key
+        for (;;) {
+            pers_bar_sync(kBarHandOver);
+            const int b = mail[0], ol = mail[1], tl = mail[2];
+            if (b < 0) break;
+            const int W = ol - tl + 1;
+            const float *links = links_all + (size_t)b * L * K;
+            const float *grow = rows_ws + (size_t)b * T * L;
+            int64_t *path = path_out + (size_t)b * L;
+            int pos = ol - 1;
+            if (lane == 0) path[pos] = tl - 1;
+            for (int t = tl - 1; t >= 1; t--) {
+                int lo = pos - K; lo = lo > t - 1 ? lo : t - 1;
+                int hi = t + W - 2; hi = hi < pos - 1 ? hi : pos - 1;
+                const float *arow = grow + (size_t)(t - 1) * L;
+                unsigned long long key = 0ull;
+                for (int i0 = lo + lane; i0 <= hi; i0 += 128) {   // four candidates requested together
+                    float a[4], e[4];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const int i = i0 + 32 * q;
+                        const bool ok = i <= hi;
+                        a[q] = ok ? __ldcg(arow + i) : -INFINITY;
+                        e[q] = ok ? __ldg(links + (size_t)i * K + (pos - i - 1)) : -INFINITY;
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const float v = __fadd_rn(a[q], e[q]);
+                        if (v > -INFINITY) {
+                            const unsigned long long kk = pack_key(v, tie_rank(pos - (i0 + 32 * q), lg));
+                            key = kk > key ? kk : key;
+                        }
+                    }
+                }
+                const unsigned hi32 = (unsigned)(key >> 32);
+                const unsigned mh = __reduce_max_sync(0xffffffffu, hi32);
+                const unsigned ml = __reduce_max_sync(0xffffffffu, hi32 == mh ? (unsigned)key : 0u);
+                if (mh == 0u && ml == 0u) break;             // cannot happen on a finite path
+                const int d = (int)((0xffffffffu - ml) & 0xfffffu);
+                if (d <= 0 || d > pos) break;
+                pos -= d;
+                if (lane == 0) path[pos] = t - 1;
+            }
+            pers_bar_arrive(kBarBacktraced);
+        }
+        return;
+    }
+
+    // ---- the sweep warps
+    float *A = reinterpret_cast<float *>(smem_raw);                    // [T][rp] rows, absolute columns
+    unsigned *P = reinterpret_cast<unsigned *>(A + (size_t)T * rp);    // [2][T][64] merged maxima of a strip
+    float *M = reinterpret_cast<float *>(P + 2 * T * 64);              // [2][T][64] match values of a strip
+    int handed = 0;
+    for (int round = 0;; round++) {
+        if (tid == 0) fetched[round & 1] = atomicAdd(counter, 1);
+        sweep_sync<kPersSweepWarps>();
+        const int q = fetched[round & 1];
+        if (q >= B) break;
+        const int b = order ? order[q] : q;
+        int64_t *path = path_out + (size_t)b * L;
+        for (int j = tid; j < L; j += kPersSweepThreads) path[j] = -1;
+        const long long oll = output_length[b], tll = target_length[b];
+        if (!lengths_valid(oll, tll, T, L)) {
+            if (tid == 0) {
+                if (max_score) max_score[b] = -INFINITY;
+                if (status) atomicOr(status, DAT_STATUS_BAD_LENGTH);
+            }
+            continue;
+        }
+        const int ol = (int)oll, tl = (int)tll;
+        const int W = ol - tl + 1;
+        const float *match = match_all + (size_t)b * T * L;
+        const float *links = links_all + (size_t)b * L * K;
+        align_strip_sweep<kPersSweepWarps>(match, links, A, P, M, ol, tl, W, T, L, K, rp, tid, lane, warp);
+        const float score = A[(size_t)(tl - 1) * rp + (ol - 1)];
+        if (tid == 0 && max_score) max_score[b] = score;
+        if (!(score > -INFINITY)) {
+            if (tid == 0 && status) atomicOr(status, DAT_STATUS_NO_PATH);
+            sweep_sync<kPersSweepWarps>();   // everyone has read the score before the next sentence clears the rows
+            continue;
+        }
+        // the rows the backtrace can ask for: steps 0 .. tl-2, the window of each
+        float *grow = rows_ws + (size_t)b * T * L;
+        for (int t = warp; t < tl - 1; t += kPersSweepWarps)
+            for (int j = t + lane; j <= t + W - 1; j += 32) grow[(size_t)t * L + j] = A[(size_t)t * rp + j];
+        __threadfence();
+        if (handed) pers_bar_sync(kBarBacktraced);   // the backtrace warp is done with the sentence before
+        if (tid == 0) {
+            mail[0] = b;
+            mail[1] = ol;
+            mail[2] = tl;
+        }
+        __threadfence_block();
+        pers_bar_arrive(kBarHandOver);
+        handed = 1;
+        sweep_sync<kPersSweepWarps>();   // (the rows are copied: the next sentence may clear them)
+    }
+    if (handed) pers_bar_sync(kBarBacktraced);
+    if (tid == 0) mail[0] = -1;
+    __threadfence_block();
+    pers_bar_arrive(kBarHandOver);
+}
+
 }  // namespace dat
 
 #include "dag_align_cluster.cuh"
@@ -527,6 +729,9 @@ namespace dat {
 static inline size_t align_smem_bytes(int L, int nrows) {
     const int pitch = align_pitch(L);
     return ((size_t)pitch * 4 + (size_t)nrows * (pitch + 32) * 4 + 15) & ~(size_t)15;
+}
+static inline size_t align_rows_bytes(int B, int T, int L) {
+    return (((size_t)B * T * L * sizeof(float)) + 255) & ~(size_t)255;
 }
 static inline size_t align_lsq_bytes(int B, int L) {
     return (((size_t)B * align_rows(L) * align_pitch(L) * sizeof(float)) + 255) & ~(size_t)255;
@@ -538,8 +743,10 @@ extern "C" {
 
 size_t dat_dag_best_alignment_workspace_bytes(int bsz, int tarlen, int prelen) {
     if (bsz <= 0 || tarlen <= 0 || prelen <= 0) return 0;
-    // square copy of the links + (only used when they do not fit in shared memory) the rows
-    return dat::align_lsq_bytes(bsz, prelen) + (size_t)bsz * tarlen * prelen * sizeof(float) + 512;
+    // square copy of the links (tiled kernel only) + the rows (every kernel but the one-sentence-per-CTA strip
+    // kernel) + the work counter and the order of the sentences (persistent strip kernel)
+    return dat::align_lsq_bytes(bsz, prelen) + dat::align_rows_bytes(bsz, tarlen, prelen) +
+           ((size_t)bsz + 64) * sizeof(int) + 512;
 }
 
 int dat_dag_best_alignment(const float *match_all, const float *links,
@@ -570,6 +777,27 @@ int dat_dag_best_alignment(const float *match_all, const float *links,
         // strip kernel: all rows plus the per-strip staging must fit in shared memory
         const int rp = (prelen + 63) & ~63;
         const size_t strip_smem = ((size_t)tarlen * rp + (size_t)4 * tarlen * 64) * sizeof(float);
+        if (strip_smem + 512 <= (size_t)di.max_smem_optin && bsz > di.sm_count) {
+            // more sentences than SMs: persistent CTAs, the backtrace of a sentence beside the sweep of the next
+            int *counter = reinterpret_cast<int *>(wbase + align_lsq_bytes(bsz, prelen) +
+                                                   align_rows_bytes(bsz, tarlen, prelen));
+            int *order = counter + 64;
+            const bool do_order = bsz <= 8192;
+            if (do_order) {
+                dag_align_order_kernel<<<1, 1024, (size_t)bsz * sizeof(float), st>>>(output_length, target_length, order,
+                                                                                     counter, bsz, tarlen, prelen);
+                if (int rc = check_launch("dat_dag_best_alignment(order)")) return rc;
+            } else if (cudaMemsetAsync(counter, 0, sizeof(int), st) != cudaSuccess) {
+                return check_launch("dat_dag_best_alignment(counter)");
+            }
+            if (cudaFuncSetAttribute(dag_align_strip_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)strip_smem) != cudaSuccess)
+                return check_launch("dat_dag_best_alignment(attr)");
+            dag_align_strip_persistent_kernel<<<(unsigned)di.sm_count, kPersThreads, strip_smem, st>>>(
+                match_all, links, output_length, target_length, do_order ? order : nullptr, counter, path, max_score,
+                rows_ws, status, bsz, tarlen, prelen, translen, lg, rp);
+            return check_launch("dat_dag_best_alignment");
+        }
         if (strip_smem + 512 <= (size_t)di.max_smem_optin) {
             if (cudaFuncSetAttribute(dag_align_strip_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)strip_smem) != cudaSuccess)

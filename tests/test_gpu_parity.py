@@ -130,6 +130,40 @@ def test_best_alignment_bit_exact(config, seed, B, L, T, K, quant):
     last_status()
 
 
+@pytest.mark.parametrize("config", [1, 3])
+@pytest.mark.parametrize("B,L,T,K,quant", [(330, 70, 12, None, 0.5), (200, 130, 40, 50, 0.0)])
+def test_best_alignment_more_sentences_than_sms(config, B, L, T, K, quant):
+    """Batches larger than the SM count run on persistent CTAs (sentences taken from a counter, the backtrace of
+    one sentence beside the sweep of the next): same paths, bit for bit, with invalid and path-less sentences among
+    them."""
+    batch = workloads.small_batch(seed=77, B=B, L=L, T=T, V=50, translen=K)
+    match, links = batch.match_all.clone(), batch.links.clone()
+    if quant:
+        match = torch.round(match / quant) * quant
+        links = torch.round(links / quant) * quant
+    ol, tl = batch.output_length.clone(), batch.target_length.clone()
+    bad = [3, 150, B - 1]
+    tl[bad[0]] = 1                 # too short a target
+    ol[bad[1]] = tl[bad[1]] - 1    # graph smaller than the target
+    ol[bad[2]] = L + 1             # beyond the padded size
+    nopath = 7
+    links[nopath, : int(ol[nopath]), :] = float("-inf")   # no transition at all: no path
+    good = [b for b in range(B) if b not in bad]
+    last_status()
+    DagBestAlignmentFunc.config = config
+    try:
+        path = dag_best_alignment(match.to(DEV), links.to(DEV), ol.to(DEV), tl.to(DEV)).cpu().numpy()
+    finally:
+        DagBestAlignmentFunc.config = 1
+    st = last_status()
+    assert st & 1 and st & 2
+    assert (path[bad] == -1).all() and (path[nopath] == -1).all()
+    good = [b for b in good if b != nopath]
+    ref, _ = oracle.dag_best_alignment(match[good].numpy(), links[good].numpy(), ol[good].numpy(), tl[good].numpy(),
+                                       dtype=np.float32, trans_block=2 ** (config + 1))
+    assert np.array_equal(path[good], ref)
+
+
 def test_all_equal_inputs_follow_the_reference_tie_break():
     B, T, L = 2, 7, 40
     match = torch.zeros(B, T, L)
