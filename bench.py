@@ -776,9 +776,11 @@ def main():
                 "regions": len(e2e_regions),
                 "how": "links uploaded without their padding (host_io.upload_links), match and lengths whole",
                 "with_whole_band_copied": {"value": e2e_full_value, "h2d_bytes_per_step": h2d_full}},
-        # per step: alignment (1: strip kernel), loss forward (4: order, strip sweep, check, exact
-        # fallback), loss backward (3: grad_match, product-form grad_links, exact fallback), statistics (1)
-        "gpu_launches": 8 * args.steps * args.repeats,
+        # per step: alignment (2 with more sentences than SMs: order, persistent strip kernel; else 1), loss forward
+        # (3: order, strip sweep with its check, exact fallback), loss backward (3: grad_match + preparation,
+        # product-form grad_links, exact fallback), statistics (1)
+        "gpu_launches": (8 + (1 if B > torch.cuda.get_device_properties(dev).multi_processor_count else 0))
+                        * args.steps * args.repeats,
         "roofline": {
             "kernel": ("dag_loss forward = dag_strip_sweep_kernel (alpha and beta recursions, one CTA each; finished "
                        "vertex groups through tcgen05 3xTF32 products, blocks inside a group as FFMAs on "

@@ -139,6 +139,9 @@ int dat_logsoftmax_gather_backward_fused(void *word_ins_out, int dtype,
  * fp64 workspace `offsets` (dat_dag_loss_offsets_bytes); only the reachable window
  * j in [t, t + ol - tl] of each row t < tl is written.
  * config: accepted for compatibility with DagLossFunc.config, ignored.
+ * Limits (checked before anything is launched, DAT_ERR_UNSUPPORTED with the limit in the message; the
+ * same for dat_dag_loss_fast and dat_dag_loss_static): prelen <= 2048, and tarlen <= 7168 when a
+ * gradient is wanted (the exact backward keeps one column of all steps in shared memory).
  */
 int dat_dag_loss(const float *match_all, const float *links, const int64_t *output_length,
                  const int64_t *target_length, int require_gradient,

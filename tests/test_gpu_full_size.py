@@ -216,7 +216,7 @@ def test_criterion_call_sequence(forced):
         o_gm[forced_t] = 0
     o_total = -np.where(bad, 0.0, o_loss / tl).mean()
     o_dx = oracle.logsoftmax_gather_backward(x64, batch.select_idx.numpy(), np.swapaxes(o_gm, 1, 2))
-    assert abs(float(loss) - o_total) <= TOL_LOSS * abs(o_total)
+    assert abs(float(loss.detach()) - o_total) <= TOL_LOSS * abs(o_total)
     assert_rel(links.grad.cpu().numpy(), o_gl, TOL_GRAD, "d loss / d links")
     assert_rel(outputs.grad.cpu().numpy(), o_dx, TOL_GRAD, "d loss / d logits")
     assert int(invalid.sum()) == int(bad.sum())
