@@ -249,17 +249,29 @@ links_fwd_warp_kernel(const float *__restrict__ content, const float *__restrict
             const int v = v0 + 32 * u;
             c4[u] = (v < nvec && !(np && !np[v / G])) ? __ldg(src + v) : ninf;
         }
+        // one new maximum per head and batch (one rescaling instead of one per element), then one ex2 per element
+        float bm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
         for (int u = 0; u < U; u++) {
-            const float c[4] = {c4[u].x * kLog2e, c4[u].y * kLog2e, c4[u].z * kLog2e, c4[u].w * kLog2e};
+            bm[0] = fmaxf(bm[0], c4[u].x);
+            bm[1] = fmaxf(bm[1], c4[u].y);
+            bm[2] = fmaxf(bm[2], c4[u].z);
+            bm[3] = fmaxf(bm[3], c4[u].w);
+        }
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                if (c[k] > m[k]) {
-                    sum[k] *= ex2(m[k] - c[k]);
-                    m[k] = c[k];
-                }
-                sum[k] += ex2(c[k] - m[k]);
+        for (int k = 0; k < 4; k++) {
+            const float b2 = bm[k] * kLog2e;
+            if (b2 > m[k]) {
+                sum[k] *= ex2(m[k] - b2);
+                m[k] = b2;
             }
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            sum[0] += ex2(fmaf(c4[u].x, kLog2e, -m[0]));
+            sum[1] += ex2(fmaf(c4[u].y, kLog2e, -m[1]));
+            sum[2] += ex2(fmaf(c4[u].z, kLog2e, -m[2]));
+            sum[3] += ex2(fmaf(c4[u].w, kLog2e, -m[3]));
         }
     }
 #pragma unroll
