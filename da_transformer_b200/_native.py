@@ -25,7 +25,7 @@ EXPORTS = (
     "dat_logsoftmax_gather_fused", "dat_logsoftmax_gather_backward_fused", "dat_sentence_mean",
     "dat_links_from_heads", "dat_links_from_heads_backward", "dat_node_passing_prob",
     "dat_viterbi_decode", "dat_viterbi_decode_workspace_bytes", "dat_dag_loss_fast_flagged",
-    "dat_upload_links", "dat_upload_links_bytes",
+    "dat_upload_links", "dat_upload_links_bytes", "dat_upload_links_head_rows",
 )
 
 _lib = None
@@ -80,6 +80,8 @@ def _declare(lib):
     lib.dat_viterbi_decode.argtypes = [_vp] * 10 + [_i32] * 4 + [ctypes.c_float, _i64, _vp]
     lib.dat_upload_links_bytes.restype = ctypes.c_size_t
     lib.dat_upload_links_bytes.argtypes = [_i32] * 4
+    lib.dat_upload_links_head_rows.restype = _i32
+    lib.dat_upload_links_head_rows.argtypes = [_i32] * 3
     lib.dat_upload_links.restype = _i32
     lib.dat_upload_links.argtypes = [_vp, _vp, _i32, _i32, _i32, _i32, _vp]
     lib.dat_logsoftmax_gather_fused.restype = _i32

@@ -10,9 +10,15 @@
 // host memory in 16-byte units (512 contiguous bytes per warp instruction) and stores it to the device
 // copy (measured: 268 MB of ragged rows at ~38 GB/s, against ~41 GB/s x 284 MB for the copy engines'
 // staircase below and 55 GB/s x 535 MB for the whole band; splitting the rows between the two made no
-// difference).  For pageable memory it falls back to the staircase of kRowBlock-row blocks, each block one strided 3-D copy over all sentences, cut
-// at the longest row of the block.
+// difference).  What does help is to keep BOTH kinds of PCIe reads going: the first rows of a sentence are nearly
+// full (row i of n has n-1-i real entries of translen), so rows 0 .. head-1, those at least three quarters real,
+// go as one contiguous block per sentence through the copy engine on a helper stream (padding included, 55 GB/s)
+// while the kernel pulls the ragged rest; the call's stream waits for both (46 GB/s over the whole transfer).
+// For pageable memory it falls back to the staircase of kRowBlock-row blocks, each block one strided 3-D copy over
+// all sentences, cut at the longest row of the block.
 #include "dat_common.cuh"
+
+#include <mutex>
 
 namespace dat {
 constexpr int kRowBlock = 32;
@@ -23,16 +29,17 @@ constexpr int kPullBlocks = 96;
 // entries (at most translen).  src and dst have the same alignment modulo 16; the units may reach a few
 // bytes into the padding on either side of the prefix, which is copied like everything else.
 __global__ void __launch_bounds__(kPullThreads)
-upload_links_pull_kernel(const float *__restrict__ src, float *__restrict__ dst, int B, int L, int K, int n) {
+upload_links_pull_kernel(const float *__restrict__ src, float *__restrict__ dst, int B, int L, int K, int n,
+                         int row_begin) {
     const int lane = threadIdx.x & 31;
     const long long nwarps = (long long)gridDim.x * (kPullThreads / 32);
-    const int per = n - 1;   // rows with a successor, in every sentence
+    const int per = n - 1 - row_begin;   // rows with a successor that this kernel moves, in every sentence
     const long long rows = (long long)B * per;
     const uintptr_t base = reinterpret_cast<uintptr_t>(src);
     const uintptr_t total = (uintptr_t)B * L * K * sizeof(float);
     const ptrdiff_t shift = reinterpret_cast<const char *>(dst) - reinterpret_cast<const char *>(src);
     for (long long w = (long long)blockIdx.x * (kPullThreads / 32) + (threadIdx.x >> 5); w < rows; w += nwarps) {
-        const int b = (int)(w / per), i = (int)(w - (long long)b * per);
+        const int b = (int)(w / per), i = row_begin + (int)(w - (long long)b * per);
         int len = n - 1 - i;
         len = len < K ? len : K;
         const uintptr_t lo = ((uintptr_t)b * L + i) * (uintptr_t)K * sizeof(float);
@@ -60,9 +67,47 @@ upload_links_pull_kernel(const float *__restrict__ src, float *__restrict__ dst,
                 *reinterpret_cast<uint4 *>(reinterpret_cast<char *>(a0 + ((uintptr_t)(k + 32 * q) << 4)) + shift) = v[q];
     }
 }
+// rows of a sentence that go through the copy engine whole: those with at least 3/4 of translen real entries
+__host__ inline int upload_head_rows(int n, int translen) {
+    int h = n - 1 - (3 * translen) / 4;
+    h = h < 0 ? 0 : h;
+    return h < n - 1 ? h : n - 1;
+}
+
+struct UploadSide {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+};
+// helper stream and events of the current device (created on first use, kept for the life of the process)
+static bool upload_side(UploadSide *out) {
+    static std::mutex mu;
+    static UploadSide side[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    std::lock_guard<std::mutex> lock(mu);
+    UploadSide &s = side[dev];
+    if (!s.stream) {
+        UploadSide t;
+        if (cudaStreamCreateWithFlags(&t.stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&t.fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&t.join, cudaEventDisableTiming) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        s = t;
+    }
+    *out = s;
+    return true;
+}
 }  // namespace dat
 
 extern "C" {
+
+int dat_upload_links_head_rows(int prelen, int translen, int max_output_length) {
+    if (prelen <= 0 || translen <= 0) return 0;
+    const int n = max_output_length < prelen ? max_output_length : prelen;
+    return n < 2 ? 0 : dat::upload_head_rows(n, translen);
+}
 
 size_t dat_upload_links_bytes(int bsz, int prelen, int translen, int max_output_length) {
     using namespace dat;
@@ -95,9 +140,32 @@ int dat_upload_links(const float *host_links, float *dev_links, int bsz, int pre
         if (!pinned) cudaGetLastError();
         if (pinned && (reinterpret_cast<uintptr_t>(mapped) & 15) == 0 &&
             (reinterpret_cast<uintptr_t>(dev_links) & 15) == 0) {
-            upload_links_pull_kernel<<<kPullBlocks, kPullThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-                static_cast<const float *>(mapped), dev_links, bsz, prelen, translen, n);
-            return check_launch("dat_upload_links");
+            cudaStream_t st = static_cast<cudaStream_t>(stream);
+            int head = upload_head_rows(n, translen);
+            UploadSide side;
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            // (not while the stream is being captured: the helper stream belongs to no graph)
+            if (head > 0 && (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone ||
+                             !upload_side(&side))) {
+                cudaGetLastError();
+                head = 0;
+            }
+            if (head > 0) {
+                const size_t sentence = (size_t)prelen * translen * sizeof(float);
+                bool ok = cudaEventRecord(side.fork, st) == cudaSuccess &&
+                          cudaStreamWaitEvent(side.stream, side.fork, 0) == cudaSuccess &&
+                          cudaMemcpy2DAsync(dev_links, sentence, host_links, sentence,
+                                            (size_t)head * translen * sizeof(float), (size_t)bsz, cudaMemcpyHostToDevice,
+                                            side.stream) == cudaSuccess &&
+                          cudaEventRecord(side.join, side.stream) == cudaSuccess;
+                if (!ok) return check_launch("dat_upload_links(copy)");
+            }
+            if (head < n - 1)
+                upload_links_pull_kernel<<<kPullBlocks, kPullThreads, 0, st>>>(static_cast<const float *>(mapped), dev_links,
+                                                                             bsz, prelen, translen, n, head);
+            if (int rc = check_launch("dat_upload_links")) return rc;
+            if (head > 0 && cudaStreamWaitEvent(st, side.join, 0) != cudaSuccess) return check_launch("dat_upload_links(join)");
+            return DAT_OK;
         }
     }
     const size_t pitch = (size_t)translen * sizeof(float);

@@ -15,13 +15,16 @@ __all__ = ["upload_links", "upload_links_bytes"]
 
 
 def upload_links_bytes(bsz, prelen, translen, max_output_length, pinned=True):
-    """Bytes ``upload_links`` moves over the bus for these sizes: the real entries of every row when the
-    source is page-locked (the rows' prefixes, each rounded to 16-byte units by the copying kernel:
-    at most 32 bytes more per row), the 32-row staircase that covers them otherwise."""
+    """Bytes ``upload_links`` moves over the bus for these sizes.  Page-locked source: the first rows of every
+    sentence whole (those at least three quarters real, copied by the copy engine) and the real entries of the
+    others (the rows' prefixes, each rounded to 16-byte units by the copying kernel: at most 32 bytes more per
+    row).  Otherwise the 32-row staircase that covers the real entries."""
     n = min(int(max_output_length), int(prelen))
     if not pinned:
         return int(lib().dat_upload_links_bytes(int(bsz), int(prelen), int(translen), n))
-    return int(bsz) * sum(min(int(translen), n - 1 - i) * 4 for i in range(max(n - 1, 0)))
+    head = int(lib().dat_upload_links_head_rows(int(prelen), int(translen), n))
+    return int(bsz) * (head * int(translen) * 4
+                       + sum(min(int(translen), n - 1 - i) * 4 for i in range(head, max(n - 1, 0))))
 
 
 def upload_links(host_links, out, max_output_length=None):

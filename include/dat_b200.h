@@ -327,11 +327,17 @@ int dat_viterbi_decode(const float *links_square, const float *unreduced_logits,
  * the entries a graph of max_output_length vertices can have; the other bytes of dev_links are left as
  * they are (give or take a few bytes of padding next to the real entries).  Page-locked host memory
  * (cudaHostAlloc / cudaHostRegister, 16-byte aligned) is read directly by a kernel on `stream`, row by
- * row; pageable memory goes through strided copies of 32-row blocks, each cut at its longest row.
- * dat_upload_links_bytes: an upper bound of the bytes that call moves over the bus (the staircase's
- * count; the kernel moves the rows' exact prefixes rounded to 16 bytes).
+ * row, except the first dat_upload_links_head_rows rows of every sentence (those with at least three
+ * quarters of translen real entries), which go whole through the copy engine on a helper stream of the
+ * library at the same time (the call's stream waits for both; while `stream` is being captured the kernel
+ * moves everything); pageable memory goes through strided copies of 32-row blocks, each cut at its
+ * longest row.
+ * dat_upload_links_bytes: an upper bound of the bytes the pageable form moves over the bus (the
+ * staircase's count).  The page-locked form moves head_rows * translen floats per sentence plus the
+ * exact prefixes of the other rows, each rounded to 16 bytes.
  */
 size_t dat_upload_links_bytes(int bsz, int prelen, int translen, int max_output_length);
+int dat_upload_links_head_rows(int prelen, int translen, int max_output_length);
 int dat_upload_links(const float *host_links, float *dev_links, int bsz, int prelen, int translen,
                      int max_output_length, void *stream);
 
