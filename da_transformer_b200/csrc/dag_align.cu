@@ -633,17 +633,20 @@ dag_align_strip_persistent_kernel(const float *__restrict__ match_all, const flo
                 int hi = t + W - 2; hi = hi < pos - 1 ? hi : pos - 1;
                 const float *arow = grow + (size_t)(t - 1) * L;
                 unsigned long long key = 0ull;
-                for (int i0 = lo + lane; i0 <= hi; i0 += 128) {   // four candidates requested together
-                    float a[4], e[4];
+                // sixteen candidates per lane requested together: a window of up to 512 vertices costs one round
+                // trip to L2 per step
+                constexpr int kBtBatch = 16;
+                for (int i0 = lo + lane; i0 <= hi; i0 += 32 * kBtBatch) {
+                    float a[kBtBatch], e[kBtBatch];
 #pragma unroll
-                    for (int q = 0; q < 4; q++) {
+                    for (int q = 0; q < kBtBatch; q++) {
                         const int i = i0 + 32 * q;
                         const bool ok = i <= hi;
                         a[q] = ok ? __ldcg(arow + i) : -INFINITY;
                         e[q] = ok ? __ldg(links + (size_t)i * K + (pos - i - 1)) : -INFINITY;
                     }
 #pragma unroll
-                    for (int q = 0; q < 4; q++) {
+                    for (int q = 0; q < kBtBatch; q++) {
                         const float v = __fadd_rn(a[q], e[q]);
                         if (v > -INFINITY) {
                             const unsigned long long kk = pack_key(v, tie_rank(pos - (i0 + 32 * q), lg));
