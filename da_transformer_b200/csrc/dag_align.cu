@@ -81,12 +81,6 @@ dag_align_prep_kernel(const float *__restrict__ links, const int64_t *__restrict
     }
 }
 
-__device__ __forceinline__ float max3(float a, float b, float c) {
-    float d;  // three-input maximum of sm_100 (NaN operands are ignored, as by fmaxf)
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-    return d;
-}
-
 // Largest 64-bit key over the CTA, returned to every thread: hardware warp reductions on the
 // two halves, one slot per warp, one CTA barrier.  `slots` alternates between two arrays from
 // one call to the next, so a slot is rewritten only after every thread has passed the barrier
@@ -322,15 +316,6 @@ __device__ __forceinline__ void strip_load_block(float (&e)[32], const float *__
             e[r] = ok ? __ldg(links + (size_t)i * K + d) : -INFINITY;
         }
     }
-}
-
-// (x, y) = (a0 + b0, a1 + b1), each rounded to nearest like __fadd_rn: the two-lane fp32 add of sm_100, one
-// issue slot for two additions (these kernels are bound by issue slots, not by the adders)
-__device__ __forceinline__ void fadd2_rn(float &x, float &y, float a0, float a1, float b0, float b1) {
-    asm("{\n\t.reg .b64 ra, rb, rc;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
-        "add.rn.f32x2 rc, ra, rb;\n\tmov.b64 {%0, %1}, rc;\n\t}"
-        : "=f"(x), "=f"(y)
-        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
 }
 
 // max over the 32 rows of a block of arow[r] + e[r]; arow is read as broadcast 16-byte loads
@@ -842,8 +827,18 @@ int dat_dag_best_alignment(const float *match_all, const float *links,
             if (ok) ok = cudaOccupancyMaxActiveClusters(&nclusters, dag_align_cluster_kernel, &ccfg) == cudaSuccess &&
                          nclusters >= 1;
             if (ok) {
+                int *counter = reinterpret_cast<int *>(wbase + align_lsq_bytes(bsz, prelen) +
+                                                       align_rows_bytes(bsz, tarlen, prelen));
+                const int *order = nullptr;
+                if (bsz > 1 && bsz <= 8192) {
+                    dag_align_order_kernel<<<1, 1024, (size_t)bsz * sizeof(float), st>>>(output_length, target_length,
+                                                                                         counter + 64, counter, bsz, tarlen,
+                                                                                         prelen);
+                    if (int rc = check_launch("dat_dag_best_alignment(order)")) return rc;
+                    order = counter + 64;
+                }
                 if (cudaLaunchKernelEx(&ccfg, dag_align_cluster_kernel, match_all, links, output_length, target_length,
-                                       path, max_score, rows_ws, status, tarlen, prelen, translen, lg) != cudaSuccess)
+                                       order, path, max_score, rows_ws, status, tarlen, prelen, translen, lg) != cudaSuccess)
                     return check_launch("dat_dag_best_alignment(cluster)");
                 return check_launch("dat_dag_best_alignment(cluster)");
             }

@@ -33,15 +33,17 @@ __host__ __device__ inline size_t align_cluster_smem_bytes(int prelen) {
 __global__ void __launch_bounds__(kClThreads, 1)
 dag_align_cluster_kernel(const float *__restrict__ match_all, const float *__restrict__ links_all,
                          const int64_t *__restrict__ output_length, const int64_t *__restrict__ target_length,
-                         int64_t *__restrict__ path_out, float *__restrict__ max_score, float *rows_ws,
-                         int32_t *__restrict__ status, int T, int L, int K, int lg) {
+                         const int *__restrict__ order, int64_t *__restrict__ path_out,
+                         float *__restrict__ max_score, float *rows_ws, int32_t *__restrict__ status, int T, int L,
+                         int K, int lg) {
     static_assert(kClThreads == kAlignThreads, "the backtrace's CTA-wide maximum assumes the alignment CTA size");
     extern __shared__ __align__(16) float acsm[];
     __shared__ unsigned long long bt_key[2][kAlignWarps];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int nranks;
     asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(nranks));
-    const int rank = (int)(blockIdx.x % nranks), b = (int)(blockIdx.x / nranks);
+    const int rank = (int)(blockIdx.x % nranks), cid = (int)(blockIdx.x / nranks);
+    const int b = order ? order[cid] : cid;   // most expensive sentences first: the clusters run in waves
     int64_t *path = path_out + (size_t)b * L;
     if (rank == 0)
         for (int j = tid; j < L; j += kClThreads) path[j] = -1;

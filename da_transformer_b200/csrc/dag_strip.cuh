@@ -109,14 +109,7 @@ __device__ __forceinline__ void strip_exp_block(float (&e)[32], int c, int h, in
         e[r] = ex2(l2);
     }
 }
-// (x, y) = (a0 * b0 + x, a1 * b1 + y), each fused and rounded to nearest like fmaf: the two-lane fp32
-// multiply-add of sm_100, one issue slot for two of them
-__device__ __forceinline__ void ffma2_rn(float &x, float &y, float a0, float a1, float b0, float b1) {
-    asm("{\n\t.reg .b64 ra, rb, rc;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%0, %1};\n\t"
-        "fma.rn.f32x2 rc, ra, rb, rc;\n\tmov.b64 {%0, %1}, rc;\n\t}"
-        : "+f"(x), "+f"(y)
-        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
-}
+// (two-lane multiply-adds: the same fused operations in half the issue slots)
 __device__ __forceinline__ float strip_block_dot(const float *yrow, const float (&e)[32]) {
     float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll

@@ -42,6 +42,35 @@ __device__ __forceinline__ float lg2(float x) {
     return y;
 }
 
+// Two-lane fp32 arithmetic of sm_100: one issue slot for two operations, each rounded like its scalar form.
+// (x, y) = (a0 + b0, a1 + b1), round to nearest like __fadd_rn
+__device__ __forceinline__ void fadd2_rn(float &x, float &y, float a0, float a1, float b0, float b1) {
+    asm("{\n\t.reg .b64 ra, rb, rc;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "add.rn.f32x2 rc, ra, rb;\n\tmov.b64 {%0, %1}, rc;\n\t}"
+        : "=f"(x), "=f"(y)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+// (x, y) = (a0 * b0 + x, a1 * b1 + y), fused and rounded to nearest like fmaf
+__device__ __forceinline__ void ffma2_rn(float &x, float &y, float a0, float a1, float b0, float b1) {
+    asm("{\n\t.reg .b64 ra, rb, rc;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%0, %1};\n\t"
+        "fma.rn.f32x2 rc, ra, rb, rc;\n\tmov.b64 {%0, %1}, rc;\n\t}"
+        : "+f"(x), "+f"(y)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+// (x, y) = (a0 * b0, a1 * b1), round to nearest
+__device__ __forceinline__ void fmul2_rn(float &x, float &y, float a0, float a1, float b0, float b1) {
+    asm("{\n\t.reg .b64 ra, rb, rc;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "mul.rn.f32x2 rc, ra, rb;\n\tmov.b64 {%0, %1}, rc;\n\t}"
+        : "=f"(x), "=f"(y)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+// three-input maximum of sm_100 (NaN operands are ignored, as by fmaxf)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

@@ -268,10 +268,11 @@ links_fwd_warp_kernel(const float *__restrict__ content, const float *__restrict
         }
 #pragma unroll
         for (int u = 0; u < U; u++) {
-            sum[0] += ex2(fmaf(c4[u].x, kLog2e, -m[0]));
-            sum[1] += ex2(fmaf(c4[u].y, kLog2e, -m[1]));
-            sum[2] += ex2(fmaf(c4[u].z, kLog2e, -m[2]));
-            sum[3] += ex2(fmaf(c4[u].w, kLog2e, -m[3]));
+            float t0 = -m[0], t1 = -m[1], t2 = -m[2], t3 = -m[3];
+            ffma2_rn(t0, t1, c4[u].x, c4[u].y, kLog2e, kLog2e);
+            ffma2_rn(t2, t3, c4[u].z, c4[u].w, kLog2e, kLog2e);
+            fadd2_rn(sum[0], sum[1], sum[0], sum[1], ex2(t0), ex2(t1));
+            fadd2_rn(sum[2], sum[3], sum[2], sum[3], ex2(t2), ex2(t3));
         }
     }
 #pragma unroll
@@ -315,23 +316,31 @@ links_fwd_warp_kernel(const float *__restrict__ content, const float *__restrict
         for (int u = 0; u < U2; u++) {
             const int d = d0 + 32 * u;
             if (d >= K) break;
+            if (d >= nj) {   // no such successor
+                out[d] = -INFINITY;
+                continue;
+            }
             float z[H];
             float mx = -INFINITY;
 #pragma unroll
             for (int gg = 0; gg < G; gg++) {
-                z[4 * gg] = fmaf(c4[u][gg].x, kLog2e, ka[4 * gg]);
-                z[4 * gg + 1] = fmaf(c4[u][gg].y, kLog2e, ka[4 * gg + 1]);
-                z[4 * gg + 2] = fmaf(c4[u][gg].z, kLog2e, ka[4 * gg + 2]);
-                z[4 * gg + 3] = fmaf(c4[u][gg].w, kLog2e, ka[4 * gg + 3]);
 #pragma unroll
-                for (int k = 0; k < 4; k++) mx = fmaxf(mx, z[4 * gg + k]);
+                for (int k = 0; k < 4; k++) z[4 * gg + k] = ka[4 * gg + k];
+                ffma2_rn(z[4 * gg], z[4 * gg + 1], c4[u][gg].x, c4[u][gg].y, kLog2e, kLog2e);
+                ffma2_rn(z[4 * gg + 2], z[4 * gg + 3], c4[u][gg].z, c4[u][gg].w, kLog2e, kLog2e);
+                mx = max3(mx, z[4 * gg], z[4 * gg + 1]);
+                mx = max3(mx, z[4 * gg + 2], z[4 * gg + 3]);
             }
             float v = -INFINITY;
             if (mx > -INFINITY) {
-                float sacc = 0.f;
+                float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-                for (int k = 0; k < H; k++) sacc += ex2(z[k] - mx);
-                v = (mx + lg2(sacc)) * kLn2;
+                for (int k = 0; k < H; k += 2) {
+                    float t0, t1;
+                    fadd2_rn(t0, t1, z[k], z[k + 1], -mx, -mx);
+                    fadd2_rn(s0, s1, s0, s1, ex2(t0), ex2(t1));
+                }
+                v = (mx + lg2(s0 + s1)) * kLn2;
             }
             out[d] = v;
         }
