@@ -49,15 +49,10 @@ __device__ __forceinline__ void online_update(float &m, float &s, const float (&
         m = vmax;
     }
     const float mneg = -m * kLog2e;
-    static_assert(N % 2 == 0, "pairs of elements");
-    float acc0 = 0.f, acc1 = 0.f;   // two-lane multiply-adds and adds: half the issue slots beside the ex2
+    float acc = 0.f;
 #pragma unroll
-    for (int i = 0; i < N; i += 2) {
-        float t0 = mneg, t1 = mneg;
-        ffma2_rn(t0, t1, f[i], f[i + 1], kLog2e, kLog2e);
-        fadd2_rn(acc0, acc1, acc0, acc1, ex2(t0), ex2(t1));
-    }
-    s += acc0 + acc1;
+    for (int i = 0; i < N; i++) acc += ex2(fmaf(f[i], kLog2e, mneg));
+    s += acc;
 }
 
 __device__ __forceinline__ void online_update1(float &m, float &s, float v) {
@@ -377,11 +372,7 @@ lsg_bwd_kernel(T *__restrict__ x, const int64_t *__restrict__ idx, Strides3 is,
                 float f[kVec];
                 Elem<T>::unpack(u[q], f);
 #pragma unroll
-                for (int i = 0; i < kVec; i += 2) {   // two-lane multiply-add and multiply beside the two ex2
-                    float t0 = c, t1 = c;
-                    ffma2_rn(t0, t1, f[i], f[i + 1], kLog2e, kLog2e);
-                    fmul2_rn(f[i], f[i + 1], ex2(t0), ex2(t1), nG, nG);
-                }
+                for (int i = 0; i < kVec; i++) f[i] = nG * ex2(fmaf(f[i], kLog2e, c));
                 xv[v + q * kLsgThreads] = Elem<T>::pack(f);
             }
         }
