@@ -226,7 +226,7 @@ __global__ void __launch_bounds__(kLwWarps * 32)
 links_fwd_warp_kernel(const float *__restrict__ content, const float *__restrict__ log_gates, LinksMask mk,
                       float *__restrict__ links, float *__restrict__ head_lse, int B, int L, int K) {
     constexpr int H = 4 * G;
-    constexpr int U = 8;   // vectors a lane has in flight
+    constexpr int U = 4;   // vectors a lane has in flight
     const int lane = threadIdx.x & 31;
     const int64_t slot = (int64_t)blockIdx.x * kLwWarps + (threadIdx.x >> 5);
     if (slot >= (int64_t)B * L) return;
@@ -394,10 +394,14 @@ links_bwd_warp_kernel(const float *__restrict__ grad_links, const float *content
 #pragma unroll
         for (int u = 0; u < U; u++) {
             if (!(l2[u] > -INFINITY)) continue;
-            const float c[4] = {c4[u].x, c4[u].y, c4[u].z, c4[u].w};
-#pragma unroll
-            for (int k = 0; k < 4; k++)
-                if (kq[k] > -INFINITY) S[k] += gd[u] * ex2(fmaf(c[k], kLog2e, kq[k]) - l2[u]);
+            // (a head that takes no part has kq = -inf: its term is ex2(-inf) = 0; two-lane arithmetic throughout)
+            float t0, t1, t2, t3;
+            fadd2_rn(t0, t1, kq[0], kq[1], -l2[u], -l2[u]);
+            fadd2_rn(t2, t3, kq[2], kq[3], -l2[u], -l2[u]);
+            ffma2_rn(t0, t1, c4[u].x, c4[u].y, kLog2e, kLog2e);
+            ffma2_rn(t2, t3, c4[u].z, c4[u].w, kLog2e, kLog2e);
+            ffma2_rn(S[0], S[1], ex2(t0), ex2(t1), gd[u], gd[u]);
+            ffma2_rn(S[2], S[3], ex2(t2), ex2(t3), gd[u], gd[u]);
         }
     }
 #pragma unroll
@@ -410,6 +414,12 @@ links_bwd_warp_kernel(const float *__restrict__ grad_links, const float *content
         for (int k = 0; k < 4; k++) grad_log_gates[row * H + 4 * g + k] = S[k];
     }
     // ---- pass 2: d/dc[j,h] = G[j] p[j,h] - exp(c[j,h] - lse_h) S_h; zeros in the rest of the dense row
+    float nl[4], nS[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        nl[k] = kq[k] > -INFINITY ? -lse2[k] : -INFINITY;
+        nS[k] = -S[k];
+    }
     for (int v0 = lane; v0 < nvec; v0 += 32 * U) {
         float4 c4[U];
         float l2[U], gd[U];
@@ -426,17 +436,24 @@ links_bwd_warp_kernel(const float *__restrict__ grad_links, const float *content
         for (int u = 0; u < U; u++) {
             const int v = v0 + 32 * u;
             if (v >= nvec) break;
-            float o[4] = {0.f, 0.f, 0.f, 0.f};
-            const float c[4] = {c4[u].x, c4[u].y, c4[u].z, c4[u].w};
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                if (c[k] > -INFINITY && kq[k] > -INFINITY) {
-                    const float soft = ex2(fmaf(c[k], kLog2e, -lse2[k]));
-                    const float pg = l2[u] > -INFINITY ? gd[u] * ex2(fmaf(c[k], kLog2e, kq[k]) - l2[u]) : 0.f;
-                    o[k] = pg - soft * S[k];
-                }
+            // soft = exp(c - lse_h) (0 for a masked score or a head that takes no part: nl = -inf there),
+            // o = G p - soft S, in two-lane arithmetic
+            float a0 = nl[0], a1 = nl[1], a2 = nl[2], a3 = nl[3];
+            ffma2_rn(a0, a1, c4[u].x, c4[u].y, kLog2e, kLog2e);
+            ffma2_rn(a2, a3, c4[u].z, c4[u].w, kLog2e, kLog2e);
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+            if (l2[u] > -INFINITY) {
+                float t0, t1, t2, t3;
+                fadd2_rn(t0, t1, kq[0], kq[1], -l2[u], -l2[u]);
+                fadd2_rn(t2, t3, kq[2], kq[3], -l2[u], -l2[u]);
+                ffma2_rn(t0, t1, c4[u].x, c4[u].y, kLog2e, kLog2e);
+                ffma2_rn(t2, t3, c4[u].z, c4[u].w, kLog2e, kLog2e);
+                fmul2_rn(o0, o1, ex2(t0), ex2(t1), gd[u], gd[u]);
+                fmul2_rn(o2, o3, ex2(t2), ex2(t3), gd[u], gd[u]);
             }
-            dst[v] = make_float4(o[0], o[1], o[2], o[3]);
+            ffma2_rn(o0, o1, ex2(a0), ex2(a1), nS[0], nS[1]);
+            ffma2_rn(o2, o3, ex2(a2), ex2(a3), nS[2], nS[3]);
+            dst[v] = make_float4(o0, o1, o2, o3);
         }
     }
     // the rest of the row: successors up to and including i, and those past jhi
