@@ -226,7 +226,7 @@ __global__ void __launch_bounds__(kLwWarps * 32)
 links_fwd_warp_kernel(const float *__restrict__ content, const float *__restrict__ log_gates, LinksMask mk,
                       float *__restrict__ links, float *__restrict__ head_lse, int B, int L, int K) {
     constexpr int H = 4 * G;
-    constexpr int U = 4;   // vectors a lane has in flight
+    constexpr int U = 8;   // vectors a lane has in flight
     const int lane = threadIdx.x & 31;
     const int64_t slot = (int64_t)blockIdx.x * kLwWarps + (threadIdx.x >> 5);
     if (slot >= (int64_t)B * L) return;
