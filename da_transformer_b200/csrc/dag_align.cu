@@ -29,7 +29,6 @@ namespace dat {
 
 constexpr int kAlignThreads = 512;
 constexpr int kAlignWarps = kAlignThreads / 32;
-constexpr int kRankNone = 0x7fffffff;
 
 __host__ __device__ inline int align_pitch(int L) { return (L + 127) & ~127; }
 __host__ __device__ inline int align_rows(int L) { return (L + 15) & ~15; }
@@ -282,7 +281,6 @@ dag_align_kernel(const float *__restrict__ match_all, const float *__restrict__ 
 // Two CTA barriers per strip instead of two per target step.
 // ---------------------------------------------------------------------------------------------
 constexpr int kStripDiagWarps = 3;
-constexpr int kStripBulkWarps = kAlignWarps - kStripDiagWarps;
 
 __device__ __forceinline__ void cp_async4(float *smem_dst, const float *gsrc) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -480,6 +478,53 @@ __device__ __forceinline__ void align_strip_sweep(const float *__restrict__ matc
     }
 }
 
+// The backtrace (dag_best_alignment.cu:185-188) by one warp.  At each step every lane re-evaluates its share of the
+// candidate predecessors of the path vertex (the same additions as the sweep's, hence the same bits) and the warp
+// keeps the largest (value, rank) key.  Sixteen candidates per lane are requested together, so a window of up to
+// 512 vertices costs one round trip to the links in L2 per step.
+// rows[t * pitch + j]: the finished rows, in global memory (kGlobalRows: written by other warps, read past L1) or
+// in shared memory.
+template <bool kGlobalRows>
+__device__ __forceinline__ void warp_backtrace(const float *rows, int pitch, const float *__restrict__ links,
+                                               int64_t *__restrict__ path, int ol, int tl, int K, int lg, int lane) {
+    const int W = ol - tl + 1;
+    int pos = ol - 1;
+    if (lane == 0) path[pos] = tl - 1;
+    for (int t = tl - 1; t >= 1; t--) {
+        int lo = pos - K; lo = lo > t - 1 ? lo : t - 1;
+        int hi = t + W - 2; hi = hi < pos - 1 ? hi : pos - 1;
+        const float *arow = rows + (size_t)(t - 1) * pitch;
+        unsigned long long key = 0ull;
+        constexpr int kBtBatch = 16;
+        for (int i0 = lo + lane; i0 <= hi; i0 += 32 * kBtBatch) {
+            float a[kBtBatch], e[kBtBatch];
+#pragma unroll
+            for (int q = 0; q < kBtBatch; q++) {
+                const int i = i0 + 32 * q;
+                const bool ok = i <= hi;
+                a[q] = ok ? (kGlobalRows ? __ldcg(arow + i) : arow[i]) : -INFINITY;
+                e[q] = ok ? __ldg(links + (size_t)i * K + (pos - i - 1)) : -INFINITY;
+            }
+#pragma unroll
+            for (int q = 0; q < kBtBatch; q++) {
+                const float v = __fadd_rn(a[q], e[q]);
+                if (v > -INFINITY) {
+                    const unsigned long long kk = pack_key(v, tie_rank(pos - (i0 + 32 * q), lg));
+                    key = kk > key ? kk : key;
+                }
+            }
+        }
+        const unsigned hi32 = (unsigned)(key >> 32);
+        const unsigned mh = __reduce_max_sync(0xffffffffu, hi32);
+        const unsigned ml = __reduce_max_sync(0xffffffffu, hi32 == mh ? (unsigned)key : 0u);
+        if (mh == 0u && ml == 0u) break;             // cannot happen on a finite path
+        const int d = (int)((0xffffffffu - ml) & 0xfffffu);
+        if (d <= 0 || d > pos) break;
+        pos -= d;
+        if (lane == 0) path[pos] = t - 1;
+    }
+}
+
 // One CTA per sentence: the sweep by all 16 warps, then the backtrace by all of them.
 __global__ void __launch_bounds__(kAlignThreads, 1)
 dag_align_strip_kernel(const float *__restrict__ match_all, const float *__restrict__ links_all,
@@ -509,14 +554,14 @@ dag_align_strip_kernel(const float *__restrict__ match_all, const float *__restr
     float *M = reinterpret_cast<float *>(P + 2 * T * 64);              // [2][T][64] match values of a strip
     align_strip_sweep<kAlignWarps>(match, links, A, P, M, ol, tl, W, T, L, K, rp, tid, lane, warp);
 
-    // backtrace (dag_best_alignment.cu:185-188).  At each step every thread re-evaluates one
-    // candidate predecessor of the path vertex; the CTA keeps the largest (value, rank) key.
     const float score = A[(size_t)(tl - 1) * rp + (ol - 1)];
     if (tid == 0 && max_score) max_score[b] = score;
     if (!(score > -INFINITY)) {
         if (tid == 0 && status) atomicOr(status, DAT_STATUS_NO_PATH);
         return;
     }
+    // the backtrace by the whole CTA: one candidate predecessor per thread and step, the CTA keeps the largest
+    // (value, rank) key (quicker than warp_backtrace when nothing else runs on the SM: 0.5 against 0.8 us a step)
     int pos = ol - 1;
     if (tid == 0) path[pos] = tl - 1;
     for (int t = tl - 1; t >= 1; t--) {
@@ -607,47 +652,10 @@ dag_align_strip_persistent_kernel(const float *__restrict__ match_all, const flo
             pers_bar_sync(kBarHandOver);
             const int b = mail[0], ol = mail[1], tl = mail[2];
             if (b < 0) break;
-            const int W = ol - tl + 1;
             const float *links = links_all + (size_t)b * L * K;
             const float *grow = rows_ws + (size_t)b * T * L;
             int64_t *path = path_out + (size_t)b * L;
-            int pos = ol - 1;
-            if (lane == 0) path[pos] = tl - 1;
-            for (int t = tl - 1; t >= 1; t--) {
-                int lo = pos - K; lo = lo > t - 1 ? lo : t - 1;
-                int hi = t + W - 2; hi = hi < pos - 1 ? hi : pos - 1;
-                const float *arow = grow + (size_t)(t - 1) * L;
-                unsigned long long key = 0ull;
-                // sixteen candidates per lane requested together: a window of up to 512 vertices costs one round
-                // trip to L2 per step
-                constexpr int kBtBatch = 16;
-                for (int i0 = lo + lane; i0 <= hi; i0 += 32 * kBtBatch) {
-                    float a[kBtBatch], e[kBtBatch];
-#pragma unroll
-                    for (int q = 0; q < kBtBatch; q++) {
-                        const int i = i0 + 32 * q;
-                        const bool ok = i <= hi;
-                        a[q] = ok ? __ldcg(arow + i) : -INFINITY;
-                        e[q] = ok ? __ldg(links + (size_t)i * K + (pos - i - 1)) : -INFINITY;
-                    }
-#pragma unroll
-                    for (int q = 0; q < kBtBatch; q++) {
-                        const float v = __fadd_rn(a[q], e[q]);
-                        if (v > -INFINITY) {
-                            const unsigned long long kk = pack_key(v, tie_rank(pos - (i0 + 32 * q), lg));
-                            key = kk > key ? kk : key;
-                        }
-                    }
-                }
-                const unsigned hi32 = (unsigned)(key >> 32);
-                const unsigned mh = __reduce_max_sync(0xffffffffu, hi32);
-                const unsigned ml = __reduce_max_sync(0xffffffffu, hi32 == mh ? (unsigned)key : 0u);
-                if (mh == 0u && ml == 0u) break;             // cannot happen on a finite path
-                const int d = (int)((0xffffffffu - ml) & 0xfffffu);
-                if (d <= 0 || d > pos) break;
-                pos -= d;
-                if (lane == 0) path[pos] = t - 1;
-            }
+            warp_backtrace<true>(grow, L, links, path, ol, tl, K, lg, lane);
             pers_bar_arrive(kBarBacktraced);
         }
         return;
