@@ -798,8 +798,8 @@ def main():
             "bound": "mufu", "achieved": sweep_rate / 1e9, "peak": mufu_peak / 1e9, "unit": "Gexp/s",
             "frac": sweep_rate / mufu_peak,
             # dram__bytes_read+write of dag_strip_sweep_kernel from the ncu capture summarised in
-            # profiles/dag_strip_sweep_c4_148sent.md (108.5 MB for 148 sentences), scaled by sentences
-            "traffic": 108.5e6 / 148 * B,
+            # profiles/dag_strip_sweep_c4_148sent.md (110.4 MB for 148 sentences), scaled by sentences
+            "traffic": 110.4e6 / 148 * B,
             "peak_kind": "measured on this device by the ex2 probe just before the timed regions",
             "nominal_peak": 16 * sm_count * peaks.get("sm_max_mhz", 1965.0) * 1e6 / 1e9,
             "algorithmic_exps_per_launch": sweep_exps, "kernel_ms": sweep_ms,

@@ -79,12 +79,13 @@ struct UploadSide {
     cudaEvent_t fork = nullptr, join = nullptr;
 };
 // helper stream and events of the current device (created on first use, kept for the life of the process)
+// (the caller holds g_upload_mutex from here until it has made its own stream wait for `join`: the events are
+// shared by all callers of a device, and a wait refers to an event's latest record)
+static std::mutex g_upload_mutex;
 static bool upload_side(UploadSide *out) {
-    static std::mutex mu;
     static UploadSide side[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
-    std::lock_guard<std::mutex> lock(mu);
     UploadSide &s = side[dev];
     if (!s.stream) {
         UploadSide t;
@@ -142,13 +143,20 @@ int dat_upload_links(const float *host_links, float *dev_links, int bsz, int pre
             (reinterpret_cast<uintptr_t>(dev_links) & 15) == 0) {
             cudaStream_t st = static_cast<cudaStream_t>(stream);
             int head = upload_head_rows(n, translen);
-            UploadSide side;
             cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
             // (not while the stream is being captured: the helper stream belongs to no graph)
-            if (head > 0 && (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone ||
-                             !upload_side(&side))) {
+            if (head > 0 && (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone)) {
                 cudaGetLastError();
                 head = 0;
+            }
+            std::unique_lock<std::mutex> lock(g_upload_mutex, std::defer_lock);
+            UploadSide side;
+            if (head > 0) {
+                lock.lock();
+                if (!upload_side(&side)) {
+                    lock.unlock();
+                    head = 0;
+                }
             }
             if (head > 0) {
                 const size_t sentence = (size_t)prelen * translen * sizeof(float);
