@@ -853,6 +853,27 @@ def extra_legs(torch, dev, ev, workloads, dag_loss, dag_best_alignment, dag_logs
     from da_transformer_b200 import last_status
 
     out = {}
+    # C0: the reference's own CPU-runnable case (B=8, L=160, T<=20, V=1000, fp32 logits), the same step as C1
+    b0 = workloads.config0().to(dev)
+    leaf0 = b0.logits.clone().requires_grad_()
+    links0 = b0.links.clone().requires_grad_()
+
+    def c0_step():
+        with torch.no_grad():
+            _, sel = dag_logsoftmax_gather_inplace(leaf0.detach(), b0.select_idx)
+            dag_best_alignment(sel.transpose(1, 2), b0.links, b0.output_length, b0.target_length)
+        work = leaf0.clone()
+        _, sel = dag_logsoftmax_gather_inplace(work, b0.select_idx)
+        loss = dag_loss(sel.transpose(1, 2), links0, b0.output_length, b0.target_length)
+        torch.autograd.grad(-(loss / b0.target_length).mean(), [leaf0, links0])
+
+    med, lo, hi = time_median(c0_step, 10)
+    out["C0"] = {"workload": f"B={b0.logits.shape[0]}, L={b0.logits.shape[1]}, T={b0.targets.shape[1]}, V={b0.logits.shape[2]}, "
+                             f"fp32 logits: gather(no grad) + alignment + gather + dag_loss fwd+bwd + gather bwd, launched "
+                             f"kernel by kernel through the Python front end (launch-bound at this size)",
+                 "ms_per_step": med, "ms_min": lo, "ms_max": hi, "sentences_per_s": b0.logits.shape[0] / (med * 1e-3)}
+    del b0, leaf0, links0
+
     # C1: B=64 ragged, fp16 logits [64, L<=512, 42000]; step = gather (no grad) + alignment + gather + loss
     # forward/backward + gather backward
     b = workloads.config1(with_logits=False)
