@@ -335,6 +335,26 @@ def test_upload_links_moves_the_real_entries_and_the_ops_never_read_the_rest():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("B,L,K,n", [(3, 96, 20, 96), (2, 130, 129, 77), (4, 64, 63, 2), (1, 40, 8, 33)])
+def test_upload_links_shapes(B, L, K, n):
+    """Narrow bands (most rows full: they go through the copy engine), graphs shorter than the padded length, the
+    smallest graph: every real entry arrives, from page-locked and from pageable memory."""
+    from da_transformer_b200 import host_io
+    g = torch.Generator().manual_seed(1000 + L + K)
+    host = torch.randn(B, L, K, generator=g).contiguous()
+    real = ((torch.arange(L).view(L, 1) + torch.arange(K).view(1, K) + 1) < n)
+    for src in (host.pin_memory(), host):
+        dev_links = torch.full(host.shape, float("nan"), device=DEV)
+        host_io.upload_links(src, dev_links, n)
+        torch.cuda.synchronize()
+        got = dev_links.cpu()
+        assert torch.equal(got[:, real], host[:, real])
+        moved = int((~torch.isnan(got)).sum()) * 4
+        claimed = host_io.upload_links_bytes(B, L, K, n, pinned=src.is_pinned())
+        assert claimed <= moved <= claimed + 32 * B * max(n - 1, 0)
+
+
+@pytest.mark.gpu
 def test_overlapped_stats_reducer_keeps_every_submission_apart():
     from da_transformer_b200 import dist as ddist
 

@@ -131,7 +131,7 @@ def test_best_alignment_bit_exact(config, seed, B, L, T, K, quant):
 
 
 @pytest.mark.parametrize("config", [1, 3])
-@pytest.mark.parametrize("B,L,T,K,quant", [(330, 70, 12, None, 0.5), (200, 130, 40, 50, 0.0)])
+@pytest.mark.parametrize("B,L,T,K,quant", [(330, 70, 12, None, 0.5), (200, 130, 40, 50, 0.0), (160, 200, 60, 30, 0.25)])
 def test_best_alignment_more_sentences_than_sms(config, B, L, T, K, quant):
     """Batches larger than the SM count run on persistent CTAs (sentences taken from a counter, the backtrace of
     one sentence beside the sweep of the next): same paths, bit for bit, with invalid and path-less sentences among
