@@ -55,4 +55,40 @@ __device__ __forceinline__ void cluster_barrier() {
     cluster_wait();
 }
 
+// Rows handed from CTA to CTA without a cluster barrier: a store into a neighbour's shared memory that counts
+// its bytes on a transaction barrier (mbarrier) of the same neighbour; the neighbour waits until the bytes it
+// expects for the step have arrived.  No release fence on the sender, no barrier among the CTAs.
+constexpr int kClRowPolls = 1 << 22;   // bound of a wait for a row (never reached)
+__device__ __forceinline__ void cluster_mbar_init(uint64_t *mbar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(mbar)), "r"(count)
+                 : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+// one arrival of this phase's only arriver, announcing the bytes the phase will receive
+__device__ __forceinline__ void cluster_mbar_expect(uint64_t *mbar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(mbar)),
+                 "r"(bytes)
+                 : "memory");
+}
+// false: gave up after kClRowPolls polls
+__device__ __forceinline__ bool cluster_mbar_wait(uint64_t *mbar, uint32_t parity) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(mbar);
+    for (int i = 0; i < kClRowPolls; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(a), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+// addr and mbar: shared::cluster addresses (cluster_map) in the same destination CTA
+__device__ __forceinline__ void cluster_st_async_b32(uint32_t addr, uint32_t v, uint32_t mbar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(addr), "r"(v),
+                 "r"(mbar)
+                 : "memory");
+}
+
 }  // namespace dat

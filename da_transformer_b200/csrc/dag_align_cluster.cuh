@@ -12,9 +12,11 @@
 //   1. every warp takes the maximum over the 32 sources of each of its blocks (the previous row lies in
 //      every CTA's shared memory) and leaves it in a slot;
 //   2. (CTA barrier) one warp per owned destination block merges the slots, adds match, and stores the new
-//      row segment into the next-row buffer of every CTA of the cluster through distributed shared memory,
-//      then (after arriving at the cluster barrier) into the rows workspace in global memory;
-//   3. (cluster barrier) the next step.
+//      row segment into the next-row buffer of every CTA of the cluster through distributed shared memory
+//      (st.async: the store counts its bytes on a transaction barrier in the destination CTA) and into the rows
+//      workspace in global memory;
+//   3. every CTA waits until the bytes of a whole row have arrived in its own buffer: no barrier among the CTAs,
+//      no release fence on the senders.
 // The additions are the reference's: one rounding per candidate (link + previous value) and one for the
 // match value, and a maximum, so the rows are bit-identical to those of the other kernels.  The backtrace is
 // the tiled kernel's, run by the cluster's first CTA on the rows workspace and the band itself.
@@ -39,6 +41,8 @@ dag_align_cluster_kernel(const float *__restrict__ match_all, const float *__res
     static_assert(kClThreads == kAlignThreads, "the backtrace's CTA-wide maximum assumes the alignment CTA size");
     extern __shared__ __align__(16) float acsm[];
     __shared__ unsigned long long bt_key[2][kAlignWarps];
+    __shared__ __align__(8) uint64_t rowbar[2];   // transaction barriers of the rows of odd and even steps
+    __shared__ int gaveup;                        // a wait for a row ran out (in rank 0: in any CTA of the cluster)
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int nranks;
     asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(nranks));
@@ -87,6 +91,11 @@ dag_align_cluster_kernel(const float *__restrict__ match_all, const float *__res
         }
     }
     for (int x = tid; x < 2 * Lp; x += kClThreads) row[x] = -INFINITY;
+    if (tid == 0) {
+        cluster_mbar_init(&rowbar[0], 1);
+        cluster_mbar_init(&rowbar[1], 1);
+        gaveup = 0;
+    }
     __syncthreads();
 
     // this warp's blocks of the link matrix, read once
@@ -130,9 +139,19 @@ dag_align_cluster_kernel(const float *__restrict__ match_all, const float *__res
     __syncthreads();
     cluster_barrier();   // every CTA of the cluster is set up before anyone writes into its shared memory
 
-    for (int t = 1; t < tl; t++) {
+    // Every destination block has one owner, and an owner sends all 32 values of a block to every CTA at every step:
+    // a CTA receives nsub * 128 bytes per step.  Steps alternate between two barriers, so bytes of step t + 2 (whose
+    // senders have seen this CTA's segments of step t + 1, hence this CTA past its wait for step t) never meet a
+    // phase that is still open for step t.
+    // Only the CTAs that own blocks take part (a short sentence in a long batch leaves some without): the others
+    // have nothing to read or send, and nobody would wait for them.
+    const uint32_t row_bytes = (uint32_t)nsub * 128u;
+    const int npairs = (nsub + 1) >> 1, nown = npairs < nranks ? npairs : nranks;
+    for (int t = 1; t < tl && rank < nown; t++) {
         const float *rowc = row + ((t - 1) & 1) * Lp;
         float *rown = row + (t & 1) * Lp;
+        uint64_t *bar = &rowbar[t & 1];
+        if (tid == 0) cluster_mbar_expect(bar, row_bytes);
         if ((t & (kClMRing / 2 - 1)) == 0) {   // match values half a ring ahead; the half before them has landed
             stage_match(t + kClMRing / 2);
             asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 1;" ::: "memory");
@@ -149,6 +168,7 @@ dag_align_cluster_kernel(const float *__restrict__ match_all, const float *__res
             if (live) slot[k * 32 + lane] = strip_block_max(rowc + 32 * c, eb[q]);
         }
         __syncthreads();
+        if (gaveup) break;   // (set during a wait, read after the barrier every thread passes next: the same for all)
         // ---- 2. the owned destination blocks, one warp each
         float o_v = -INFINITY;
         bool o_inside = false;
@@ -165,19 +185,29 @@ dag_align_cluster_kernel(const float *__restrict__ match_all, const float *__res
                 v = __fadd_rn(best, M[((t & (kClMRing - 1)) * kClMaxDest + warp) * 32 + lane]);
                 if (!(v > -INFINITY) || !inside) v = -INFINITY;
             }
-            for (int r = 0; r < nranks; r++) cluster_st_f32(cluster_map(rown + u, r), v);
+            for (int r = 0; r < nown; r++)
+                cluster_st_async_b32(cluster_map(rown + u, r), __float_as_uint(v), cluster_map(bar, r));
             o_v = v;
             o_inside = inside;
             o_u = u;
         }
-        cluster_arrive();
-        if (o_inside) grow[(size_t)t * L + o_u] = o_v;   // (after the arrival: a whole step to complete)
-        // ---- 3. the next row is complete everywhere
-        cluster_wait();
+        if (o_inside) grow[(size_t)t * L + o_u] = o_v;
+        // ---- 3. the next row is complete here (every CTA waits for its own copy only)
+        // (the barrier of this step's parity has been through (t + 1) / 2 - 1 phases before this one)
+        if (!cluster_mbar_wait(bar, (uint32_t)((((t + 1) >> 1) + 1) & 1))) gaveup = 1;
     }
+    __syncthreads();
+    if (gaveup && tid == 0 && rank != 0) cluster_st_s32(cluster_map(&gaveup, 0), 1);
     __threadfence();
     cluster_barrier();   // every row is in the workspace; nobody leaves while a neighbour may still write here
     if (rank != 0) return;
+    if (gaveup) {   // cannot happen: a wait for a row ran out somewhere in the cluster; the sentence gets no path
+        if (tid == 0) {
+            if (max_score) max_score[b] = -INFINITY;
+            if (status) atomicOr(status, DAT_STATUS_NO_PATH);
+        }
+        return;
+    }
 
     // backtrace (dag_best_alignment.cu:185-188): at each step every thread re-evaluates one candidate
     // predecessor of the path vertex; the CTA keeps the largest (value, rank) key
