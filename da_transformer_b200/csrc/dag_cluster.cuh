@@ -15,12 +15,15 @@
 //      are finished by one warp each: the partial sums are added in a unit chosen from their magnitudes,
 //      multiplied by exp(match), renormalised to one power-of-two exponent per 32 vertices, written to the
 //      output (log2 value relative to a row offset known before the step) and to the next-row buffer of all
-//      CTAs of the cluster through distributed shared memory;
-//   3. (cluster barrier) the next step.
+//      CTAs of the cluster through distributed shared memory (st.async: a store counts its bytes on a
+//      transaction barrier in the destination CTA);
+//   3. every CTA waits until the bytes of a whole row have arrived in its own buffers, then the next step: no
+//      barrier among the CTAs, no release fence on the senders.
 // Numerics and outputs are those of the strip sweep: fp32 mantissas with one exponent per sub-strip and step,
 // units within 2^64 of the largest term, inputs below 2^-120 and holes reported through the sentence's
 // flag word, log2 maxima per (step, sub-strip) and per step for dag_fast_check_kernel.  Nothing waits on a
-// flag: the only synchronisation is the hardware barrier of the CTA and of the cluster.
+// flag: the synchronisation is the hardware barrier of the CTA and the transaction barriers of the rows (bounded
+// waits; a sentence whose wait ran out would go to the exact kernels).
 // A step here costs about as much time as the strip sweep's four iterations for the same step and occupies
 // several SMs, so on sentences whose rows fit in one SM's shared memory the strip sweep has twice the
 // throughput (1.3 against 6.7 ms for 512 sentences of 512 vertices).  This kernel is for the sentences that
@@ -56,6 +59,8 @@ dag_cluster_sweep_kernel(const float *__restrict__ match_all, const float *__res
                          int *__restrict__ flag, float *__restrict__ loss, int32_t *__restrict__ status, int T, int L,
                          int K, int nH) {
     extern __shared__ __align__(16) float csm[];
+    __shared__ __align__(8) uint64_t rowbar[2];   // transaction barriers of the rows of odd and even steps
+    __shared__ int gaveup;                        // a wait for a row ran out
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int nranks;
     asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(nranks));
@@ -113,6 +118,11 @@ dag_cluster_sweep_kernel(const float *__restrict__ match_all, const float *__res
     for (int x = tid; x < 2 * Lp; x += kClThreads) sm.row[x] = 0.f;
     for (int x = tid; x < 2 * kClMaxSub; x += kClThreads) sm.ex[x] = kExpNone;
     for (int x = tid; x < 4 * kClMaxSub; x += kClThreads) sm.mx[x] = -INFINITY;
+    if (tid == 0) {
+        cluster_mbar_init(&rowbar[0], 1);
+        cluster_mbar_init(&rowbar[1], 1);
+        gaveup = 0;
+    }
     __syncthreads();
 
     // ---- this warp's blocks of E, read and exponentiated once
@@ -184,10 +194,18 @@ dag_cluster_sweep_kernel(const float *__restrict__ match_all, const float *__res
     __syncthreads();
     cluster_barrier();   // every CTA of the cluster is set up before anyone writes into its shared memory
 
-    for (int s = 1; s < tl; s++) {
+    // Every destination block has one owner, which sends the block's 32 values and three words (exponent, two
+    // maxima) to every CTA that takes part, at every step: nsub * 140 bytes per CTA and step, counted by a
+    // transaction barrier of the receiving CTA; steps alternate between two barriers.  Only the CTAs that own blocks
+    // take part (a short sentence in a long batch leaves some without).
+    const uint32_t row_bytes = (uint32_t)nsub * 140u;
+    const int npairs = (nsub + 1) >> 1, nown = npairs < nranks ? npairs : nranks;
+    for (int s = 1; s < tl && rank < nown; s++) {
         const int cur = (s - 1) & 1, nxt = s & 1;
         const float *rowc = sm.row + cur * Lp;
         const int *exc = sm.ex + cur * kClMaxSub;
+        uint64_t *bar = &rowbar[s & 1];
+        if (tid == 0) cluster_mbar_expect(bar, row_bytes);
         if ((s & (kClMRing / 2 - 1)) == 0) {   // match values half a ring ahead; the half before them has landed
             stage_match(s + kClMRing / 2);
             asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 1;" ::: "memory");
@@ -221,10 +239,8 @@ dag_cluster_sweep_kernel(const float *__restrict__ match_all, const float *__res
             if (lane == 0) sm.slotmag[k] = (live && pb != 0u) ? exponent_of_bits(pb) + ec : kExpNone;
         }
         __syncthreads();
-        // ---- 2. the owned destination blocks, one warp each.  The arrival at the cluster barrier (a release of
-        // everything written so far) comes right after the stores into the neighbours' shared memory and BEFORE
-        // this step's stores to global memory: those then have a whole step to complete instead of holding
-        // the barrier up.
+        if (gaveup) break;   // (set during a wait, read after the barrier every thread passes next: the same for all)
+        // ---- 2. the owned destination blocks, one warp each
         float o_val = 0.f, o_hyv = 0.f;
         bool o_inside = false;
         int o_off = 0, o_d = 0;
@@ -279,9 +295,10 @@ dag_cluster_sweep_kernel(const float *__restrict__ match_all, const float *__res
                              : lane == 1 ? (const void *)(sm.mx + (nxt * 2 + 0) * kClMaxSub + d)
                                          : (const void *)(sm.mx + (nxt * 2 + 1) * kClMaxSub + d);
             const int metav = lane == 0 ? e : lane == 1 ? __float_as_int(hy) : __float_as_int(hv);
-            for (int r = 0; r < nranks; r++) {
-                cluster_st_f32(cluster_map(rown, r), y);
-                if (lane < 3) cluster_st_s32(cluster_map(meta, r), metav);
+            for (int r = 0; r < nown; r++) {
+                const uint32_t rbar = cluster_map(bar, r);
+                cluster_st_async_b32(cluster_map(rown, r), __float_as_uint(y), rbar);
+                if (lane < 3) cluster_st_async_b32(cluster_map(meta, r), (uint32_t)metav, rbar);
             }
             // the output row: log2 values relative to the row offset
             o_off = offe != kExpNone ? offe : 0;
@@ -290,7 +307,6 @@ dag_cluster_sweep_kernel(const float *__restrict__ match_all, const float *__res
             o_hyv = rev ? hv : hy;
             o_d = d;
         }
-        cluster_arrive();
         if (warp < nd) {
             const int t = rev ? tl - 1 - s : s, u = 32 * o_d + lane;
             if (o_inside) out[(size_t)t * L + (rev ? ol - 1 - u : u)] = o_val;
@@ -299,9 +315,11 @@ dag_cluster_sweep_kernel(const float *__restrict__ match_all, const float *__res
                 if (o_d == 0) offs[(rev ? T : 0) + t] = (double)o_off;   // (block 0 belongs to rank 0)
             }
         }
-        // ---- 3. the next row is complete everywhere
-        cluster_wait();
+        // ---- 3. the next row is complete here (every CTA waits for its own copy only)
+        if (!cluster_mbar_wait(bar, (uint32_t)((((s + 1) >> 1) + 1) & 1))) gaveup = 1;
     }
+    __syncthreads();
+    if (gaveup && tid == 0) atomicOr(flag + b, kFlagTiny);   // cannot happen; the exact kernels take the sentence
     // ---- the last step's maxima, the sub-strips nobody owns, the likelihood
     {
         const int last = (tl - 1) & 1;
