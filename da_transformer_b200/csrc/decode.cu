@@ -80,13 +80,15 @@ viterbi_decode_kernel(const float *__restrict__ links_all, const float *__restri
                       int64_t *__restrict__ out_length, int64_t *__restrict__ out_vertices,
                       float *__restrict__ out_score, int32_t *__restrict__ status, int L, int max_length,
                       int joint, float beta, int64_t pad) {
-    extern __shared__ float vsm[];
+    extern __shared__ __align__(16) float vsm[];
     const int Lp = (L + 31) & ~31;
     float *a0 = vsm, *a1 = vsm + Lp;            // alpha of two consecutive steps
     float *lastcol = a1 + Lp;                    // links[j][ol-1]
     float *lg = lastcol + Lp;                    // token log-probabilities of the vertices
     float *part_v = lg + Lp;                     // [2][Lp] partial winners of a step's columns
     int *part_i = reinterpret_cast<int *>(part_v + 2 * Lp);
+    unsigned char *step_plain = reinterpret_cast<unsigned char *>(part_i + 2 * Lp);   // [max_length] kind of a step
+    __shared__ unsigned long long bt_slot[2][kDecWarps];
     __shared__ float red_v[kDecWarps];
     __shared__ int red_i[kDecWarps];
     __shared__ float best_score;
@@ -123,10 +125,19 @@ viterbi_decode_kernel(const float *__restrict__ links_all, const float *__restri
     }
     // A transition matrix as decoding builds it has -inf on and below its diagonal; the recursion then
     // only needs the candidates i < j (checked once here: any other matrix takes all L candidates).
-    bool dense = false;
+    bool dense = false, dirty = false;   // dirty: a NaN or +inf transition (a sum with it can be NaN)
     for (int i = warp; i < L; i += kDecWarps)
-        for (int j = lane; j <= i; j += 32) dense |= !(__ldg(lk + (size_t)i * L + j) == -INFINITY);
+        for (int j = lane; j < L; j += 32) {
+            const float e = __ldg(lk + (size_t)i * L + j);
+            if (j <= i) dense |= !(e == -INFINITY);
+            else dirty |= !(e < INFINITY);
+        }
     const bool upper = !__syncthreads_or(dense);
+    // A step is "plain" when the matrix is triangular and clean and the current row has no +inf or NaN: no sum can
+    // be NaN then, torch.max is an ordinary maximum with the first index among equals, and the step keeps only the
+    // VALUES of its row (in place of the back-pointers); the back-trace finds the predecessor of the one vertex per
+    // step that lies on the path by re-evaluating its candidates (the same additions, the same bits).
+    const bool clean = upper && !__syncthreads_or(dirty);
     for (int t = 0; t < max_length; t++) {
         const float *cur = (t & 1) ? a1 : a0;
         float *nxt = (t & 1) ? a0 : a1;
@@ -173,6 +184,8 @@ viterbi_decode_kernel(const float *__restrict__ links_all, const float *__restri
         if (upper)
             for (int i = tid; i < L; i += kDecThreads) odd |= !(cur[i] < INFINITY);
         const bool tri = upper && !__syncthreads_or(odd);
+        const bool plain = tri && clean;
+        if (tid == 0) step_plain[t] = plain ? 1 : 0;
         // The matrix is walked in 32 x 32 tiles (lane = destination j, 32 sources per tile, all of a tile's
         // loads in flight together, two tiles at a time).  Column block c has c + 1 tiles when the matrix is
         // triangular, so blocks c and nb-1-c form a pair of nb + 1 tiles, and the two warps of a warp pair
@@ -199,6 +212,36 @@ viterbi_decode_kernel(const float *__restrict__ links_all, const float *__restri
                     int bi = INT_MAX;
                     bool nan = false;
                     const float *col = lk + (j < L ? j : 0);
+                    if (plain) {   // values only: an add and half a three-input maximum per candidate
+                        for (int rb = r0; rb < r1; rb += 2) {
+                            float v[64];
+                            const bool two = rb + 1 < r1;
+#pragma unroll
+                            for (int u = 0; u < 32; u++) {
+                                const int i = 32 * rb + u;
+                                v[u] = (i < L && j < L && i < j) ? __ldg(col + (size_t)i * L) : -INFINITY;
+                            }
+#pragma unroll
+                            for (int u = 0; u < 32; u++) {
+                                const int i = 32 * (rb + 1) + u;
+                                v[32 + u] = (two && i < L && j < L && i < j) ? __ldg(col + (size_t)i * L) : -INFINITY;
+                            }
+                            const float *crow = cur + 32 * rb;   // (the row buffer is padded to a multiple of 32 with
+                            float m0 = -INFINITY, m1 = -INFINITY;   //  -inf and has 32 more floats behind it)
+#pragma unroll
+                            for (int q = 0; q < 16; q++) {
+                                const float4 a = *reinterpret_cast<const float4 *>(crow + 4 * q);
+                                float s0, s1, s2, s3;
+                                fadd2_rn(s0, s1, a.x, a.y, v[4 * q], v[4 * q + 1]);
+                                fadd2_rn(s2, s3, a.z, a.w, v[4 * q + 2], v[4 * q + 3]);
+                                m0 = max3(m0, s0, s1);
+                                m1 = max3(m1, s2, s3);
+                            }
+                            bv = max3(bv, m0, m1);
+                        }
+                        if (j < L) part_v[hf * Lp + j] = bv;
+                        continue;
+                    }
                     for (int rb = r0; rb < r1; rb += 2) {
                         float v[64];
                         const bool two = rb + 1 < r1;
@@ -233,6 +276,16 @@ viterbi_decode_kernel(const float *__restrict__ links_all, const float *__restri
             }
         }
         __syncthreads();
+        if (plain) {
+            float *rowvals = reinterpret_cast<float *>(trace + (size_t)t * L);
+            for (int j = tid; j < L; j += kDecThreads) {
+                const float bv = fmaxf(part_v[j], part_v[Lp + j]);
+                rowvals[j] = cur[j];                 // what the back-trace needs of this step
+                nxt[j] = joint ? bv + lg[j] : bv;
+            }
+            __syncthreads();
+            continue;
+        }
         for (int j = tid; j < L; j += kDecThreads) {
             float bv = part_v[j];
             int bi = part_i[j];
@@ -249,16 +302,47 @@ viterbi_decode_kernel(const float *__restrict__ links_all, const float *__restri
     }
     __syncthreads();
     // ---- back-trace and token collapse by one thread (<= max_length steps; :757-771)
-    if (tid == 0) {
-        const int len = best_len;
-        int64_t *vert = out_vertices + (size_t)b * max_length;
-        int64_t *tok = out_tokens + (size_t)b * max_length;
-        const int64_t *tokens = tokens_all + (size_t)b * L;
+    const int len = best_len;
+    int64_t *vert = out_vertices + (size_t)b * max_length;
+    {
+        // back-trace.  A step that kept back-pointers is one lookup; a plain step kept its row, and the predecessor
+        // of vertex j is the first index of the maximum of row[i] + links[i][j] over all i (torch.max's order:
+        // larger value, then smaller index; -0 and +0 are equal), found by the whole CTA.
         int j = best_vertex;
         for (int k = len - 1; k >= 0; k--) {
-            vert[k] = j;
-            if (k > 0) j = trace[(size_t)(k - 1) * L + j];
+            if (tid == 0) vert[k] = j;
+            if (k == 0) break;
+            if (!step_plain[k - 1]) {
+                j = trace[(size_t)(k - 1) * L + j];
+                continue;
+            }
+            const float *rowvals = reinterpret_cast<const float *>(trace + (size_t)(k - 1) * L);
+            unsigned long long key = 0ull;
+            for (int i = tid; i < L; i += kDecThreads) {
+                float w = rowvals[i] + __ldg(lk + (size_t)i * L + j);
+                w += 0.0f;
+                const unsigned u = __float_as_uint(w);
+                const unsigned ord = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+                const unsigned long long kk = ((unsigned long long)ord << 32) | (0xffffffffu - (unsigned)i);
+                key = kk > key ? kk : key;
+            }
+            const unsigned hi = (unsigned)(key >> 32);
+            const unsigned mh = __reduce_max_sync(0xffffffffu, hi);
+            const unsigned ml = __reduce_max_sync(0xffffffffu, hi == mh ? (unsigned)key : 0u);
+            unsigned long long *slots = bt_slot[k & 1];
+            if (lane == 0) slots[warp] = ((unsigned long long)mh << 32) | ml;
+            __syncthreads();
+            const unsigned long long kw = lane < kDecWarps ? slots[lane] : 0ull;
+            const unsigned kh = (unsigned)(kw >> 32);
+            const unsigned wh = __reduce_max_sync(0xffffffffu, kh);
+            const unsigned wl = __reduce_max_sync(0xffffffffu, kh == wh ? (unsigned)kw : 0u);
+            j = (int)(0xffffffffu - wl);
         }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int64_t *tok = out_tokens + (size_t)b * max_length;
+        const int64_t *tokens = tokens_all + (size_t)b * L;
         for (int k = len; k < max_length; k++) vert[k] = -1;
         // walk from the end: a token is kept unless it is pad or equals the token that follows it;
         // the final token is always kept.  Kept tokens are written right-aligned, then shifted left.
@@ -314,7 +398,7 @@ int dat_viterbi_decode(const float *links_square, const float *unreduced_logits,
                     out_tokens && out_length && out_vertices && out_score,
                 DAT_ERR_BAD_ARG, "%s: null pointer", who);
     DAT_REQUIRE(prelen <= 4096, DAT_ERR_UNSUPPORTED, "%s: prelen=%d exceeds 4096", who, prelen);
-    const size_t smem = (size_t)8 * ((prelen + 31) & ~31) * sizeof(float);
+    const size_t smem = (size_t)8 * ((prelen + 31) & ~31) * sizeof(float) + (((size_t)max_length + 15) & ~(size_t)15);
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(viterbi_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
             cudaSuccess)

@@ -292,6 +292,28 @@ def test_viterbi_decode_matches_oracle_at_decoding_size(joint, beta):
     assert last_status() == 0
 
 
+@pytest.mark.parametrize("joint", [False, True])
+def test_viterbi_decode_ties_take_the_first_index(joint):
+    """Coarsely quantised scores make many candidates tie exactly: the predecessor is torch.max's (the first index of
+    the maximum), also where a step keeps only its row and the back-trace re-evaluates the candidates."""
+    gen = torch.Generator().manual_seed(23)
+    B, L, V, scale = 4, 192, 17, 8
+    ol = torch.tensor([192, 100, 191, 33])
+    sq = workloads.band_to_square(workloads.make_links(B, L, ol, gen))
+    sq = torch.where(torch.isfinite(sq), torch.round(sq * 2) / 2, sq)
+    logp = torch.log_softmax(torch.randn(B, L, V, generator=gen), -1)
+    ul, ut = logp.max(-1)
+    ul = torch.round(ul * 2) / 2
+    max_length = int(2 * L / scale)
+    toks, lens, verts, score = dag_viterbi_decode(sq.to(DEV), (ul.to(DEV), ut.to(DEV)), ol.to(DEV), max_length,
+                                                  joint=joint, viterbibeta=1.0, pad_index=1)
+    rt, rl, rv, rs = oracle.viterbi_decode(sq.numpy(), ul.numpy(), ut.numpy(), ol.numpy(), max_length, joint=joint,
+                                           beta=1.0, pad=1)
+    assert np.array_equal(verts.cpu().numpy(), rv)
+    assert np.array_equal(toks.cpu().numpy(), rt) and np.array_equal(lens.cpu().numpy(), rl)
+    assert_rel(score.cpu().numpy(), rs, 1e-5, "score")
+
+
 # ----------------------------------------------------------------------------- host upload
 def test_upload_links_moves_the_real_entries_and_the_ops_never_read_the_rest():
     """The band's padding is not transferred; the device copy keeps NaN there, and loss, gradients and
