@@ -12,7 +12,9 @@
 //   dat_viterbi_decode: GlatDecomposedLink.inference_viterbi (glat_decomposed_with_link.py:720-777):
 //     max-plus recursion over the number of emitted tokens with back-pointers, the length-normalised
 //     choice of the best length, the back-trace and the collapse of repeated / pad tokens, all on the
-//     device (the reference back-traces in Python lists on the host).
+//     device (the reference back-traces in Python lists on the host).  A step whose sums cannot be NaN (triangular
+//     matrix without NaN or +inf, row without +inf or NaN) keeps its row's values instead of back-pointers; the
+//     back-trace re-evaluates the candidates of the vertices on the path.
 // One CTA per sentence; the matrix of a sentence (<= 4 MB) is served by L2 after its first read.
 #include <climits>
 

@@ -311,7 +311,7 @@ int dat_node_passing_prob(const float *links_square, float *node_pass, int bsz, 
  * (repeated and pad tokens dropped as in :762-769); out_length [bsz] its length; out_vertices
  * [bsz,max_length] the vertices of the best path before the collapse (-1 padded); out_score [bsz] the
  * length-normalised score.  Maxima resolve ties to the first index like torch.max.
- * workspace: dat_viterbi_decode_workspace_bytes(...) bytes (the back-pointers).  prelen <= 4096.
+ * workspace: dat_viterbi_decode_workspace_bytes(...) bytes (per step the back-pointers or the row's values).  prelen <= 4096.
  */
 size_t dat_viterbi_decode_workspace_bytes(int bsz, int prelen, int max_length);
 int dat_viterbi_decode(const float *links_square, const float *unreduced_logits,
