@@ -146,8 +146,10 @@ viterbi_decode_kernel(const float *__restrict__ links_all, const float *__restri
         // ---- score of stopping after t+1 tokens: max_j cur[j] + links[j][last], first maximum (:747-752)
         float sv = -INFINITY;
         int si = INT_MAX;
+        bool odd = false;   // a +inf or NaN in the row (looked for in the same pass)
         for (int j = tid; j < L; j += kDecThreads) {
             const float v = cur[j] + lastcol[j];
+            odd |= !(cur[j] < INFINITY);
             if (v != v) { sv = v; si = j < si ? j : si; }   // NaN counts as the maximum, like torch.max
             else if (!(sv != sv)) vit_better(sv, si, v, j);
         }
@@ -159,7 +161,7 @@ viterbi_decode_kernel(const float *__restrict__ links_all, const float *__restri
             else if (!(sv != sv)) vit_better(sv, si, ov, oi);
         }
         if (lane == 0) { red_v[warp] = sv; red_i[warp] = si; }
-        __syncthreads();
+        const bool any_odd = __syncthreads_or(odd);   // (also the barrier between the warps' results and their merge)
         if (tid == 0) {
             float v = red_v[0];
             int i = red_i[0];
@@ -182,10 +184,7 @@ viterbi_decode_kernel(const float *__restrict__ links_all, const float *__restri
         // ---- next step: nxt[j] = max_i cur[i] + links[i][j], first maximum (:737-742).  With an upper
         // triangular matrix the candidates i >= j are -inf + cur[i]: they never win, unless cur[i] is +inf or
         // NaN (the sum is NaN then, and torch.max returns the first NaN), so such a step takes all L.
-        bool odd = false;
-        if (upper)
-            for (int i = tid; i < L; i += kDecThreads) odd |= !(cur[i] < INFINITY);
-        const bool tri = upper && !__syncthreads_or(odd);
+        const bool tri = upper && !any_odd;
         const bool plain = tri && clean;
         if (tid == 0) step_plain[t] = plain ? 1 : 0;
         // The matrix is walked in 32 x 32 tiles (lane = destination j, 32 sources per tile, all of a tile's
