@@ -18,6 +18,7 @@
 // One CTA per sentence; the matrix of a sentence (<= 4 MB) is served by L2 after its first read.
 #include <climits>
 
+#include "cluster_util.cuh"
 #include "dat_common.cuh"
 
 namespace dat {
@@ -80,8 +81,10 @@ viterbi_decode_kernel(const float *__restrict__ links_all, const float *__restri
                       const int64_t *__restrict__ tokens_all, const int64_t *__restrict__ output_length,
                       int32_t *__restrict__ trace_all, int64_t *__restrict__ out_tokens,
                       int64_t *__restrict__ out_length, int64_t *__restrict__ out_vertices,
-                      float *__restrict__ out_score, int32_t *__restrict__ status, int L, int max_length,
-                      int joint, float beta, int64_t pad) {
+                      float *__restrict__ out_score, int32_t *__restrict__ status,
+                      const int *__restrict__ select, int L, int max_length, int joint, float beta, int64_t pad) {
+    // select (optional): only the sentences with a non-zero word are decoded here (the cluster kernel has done the others)
+    if (select != nullptr && select[blockIdx.x] == 0) return;
     extern __shared__ __align__(16) float vsm[];
     const int Lp = (L + 31) & ~31;
     float *a0 = vsm, *a1 = vsm + Lp;            // alpha of two consecutive steps
@@ -363,6 +366,284 @@ viterbi_decode_kernel(const float *__restrict__ links_all, const float *__restri
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Viterbi decoding of one sentence by a thread-block cluster.  The general kernel above reads the whole
+// upper triangle of the matrix from L2 once per emitted token; here the triangle sits in the registers of a
+// cluster of 4, 8 or 16 CTAs (32 x 32 blocks, lane = destination, up to three blocks per warp, destination
+// blocks dealt to the CTAs in pairs of equal work: the layout of the training kernels for long sentences) and
+// is read once per call.  A step: every warp takes the maximum over the 32 sources of each of its blocks
+// (the current row lies in every CTA's shared memory), one warp per owned destination block merges them,
+// adds the token score and hands the new 32 values to every CTA (st.async onto the receivers' transaction
+// barriers) and to the workspace; every CTA waits for its own copy of the row.  Only VALUES are kept; the
+// back-trace re-evaluates the candidates of the vertices on the path (first index of the maximum, like
+// torch.max).  That is valid when no sum can be NaN: matrix -inf on and below the diagonal, no NaN or +inf
+// above it, no +inf or NaN in any row.  The kernel checks all three while it runs and raises the sentence's
+// word in `redo` otherwise; the general kernel then decodes that sentence again with torch's NaN rules.
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ inline size_t viterbi_cluster_smem_bytes(int L) {
+    const int Lp = (L + 31) & ~31;
+    return (size_t)(3 * Lp + kClMaxBlocks * 32 + kClMaxDest * 32 + 2 * kClMaxBlocks + 2 * kClMaxDest) * sizeof(float) + 64;
+}
+
+__device__ __forceinline__ float vit_block_max(const float *arow, const float (&e)[32]) {
+    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+    for (int q = 0; q < 8; q += 2) {
+        const float4 a = *reinterpret_cast<const float4 *>(arow + 4 * q);
+        const float4 c = *reinterpret_cast<const float4 *>(arow + 4 * q + 4);
+        float s0, s1, s2, s3, s4, s5, s6, s7;
+        fadd2_rn(s0, s1, a.x, a.y, e[4 * q], e[4 * q + 1]);
+        fadd2_rn(s2, s3, a.z, a.w, e[4 * q + 2], e[4 * q + 3]);
+        fadd2_rn(s4, s5, c.x, c.y, e[4 * q + 4], e[4 * q + 5]);
+        fadd2_rn(s6, s7, c.z, c.w, e[4 * q + 6], e[4 * q + 7]);
+        m0 = max3(m0, s0, s1);
+        m1 = max3(m1, s2, s3);
+        m2 = max3(m2, s4, s5);
+        m3 = max3(m3, s6, s7);
+    }
+    return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+
+__global__ void __launch_bounds__(kClThreads, 1)
+viterbi_cluster_kernel(const float *__restrict__ links_all, const float *__restrict__ logits_all,
+                       const int64_t *__restrict__ tokens_all, const int64_t *__restrict__ output_length,
+                       float *rows_all, int *redo, int64_t *__restrict__ out_tokens,
+                       int64_t *__restrict__ out_length, int64_t *__restrict__ out_vertices,
+                       float *__restrict__ out_score, int32_t *__restrict__ status, int L, int max_length, int joint,
+                       float beta, int64_t pad) {
+    extern __shared__ __align__(16) float vcs[];
+    __shared__ __align__(8) uint64_t rowbar[2];
+    __shared__ int gaveup;
+    __shared__ unsigned long long bt_slot[2][kClWarps];
+    __shared__ float best_score;
+    __shared__ int best_len, best_vertex;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int nranks;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(nranks));
+    const int rank = (int)(blockIdx.x % nranks), b = (int)(blockIdx.x / nranks);
+    const float *lk = links_all + (size_t)b * L * L;
+    const float *logit = logits_all + (size_t)b * L;
+    float *rows = rows_all + (size_t)b * (max_length > 1 ? max_length - 1 : 1) * L;
+    const long long oll = output_length[b];
+    if (oll < 1 || oll > L) {   // the same for every CTA of the cluster: nobody reaches a cluster barrier
+        if (rank == 0) {
+            if (tid == 0) {
+                if (status) atomicOr(status, DAT_STATUS_BAD_LENGTH);
+                out_length[b] = 0;
+                out_score[b] = -INFINITY;
+                redo[b] = 0;
+            }
+            for (int k = tid; k < max_length; k += kClThreads) {
+                out_tokens[(size_t)b * max_length + k] = pad;
+                out_vertices[(size_t)b * max_length + k] = -1;
+            }
+        }
+        return;
+    }
+    const int last = (int)oll - 1;
+    const int Lp = (L + 31) & ~31, nsub = Lp >> 5;
+    float *row = vcs;                                   // [2][Lp] current / next row (-inf past L)
+    float *lastcol = row + 2 * Lp;                      // [Lp] links[j][last] (used by the first CTA)
+    float *slot = lastcol + Lp;                         // [kClMaxBlocks][32] maxima of this CTA's blocks
+    float *lgs = slot + kClMaxBlocks * 32;              // [kClMaxDest][32] token scores of the owned destinations
+    int *tab_c = reinterpret_cast<int *>(lgs + kClMaxDest * 32);
+    int *tab_d = tab_c + kClMaxBlocks;
+    int *dlist = tab_d + kClMaxBlocks;
+    int *dbase = dlist + kClMaxDest;
+
+    int nd = 0, nblk = 0;
+    for (int p = rank; 2 * p < nsub; p += nranks) {
+        for (int side = 0; side < 2; side++) {
+            const int d = side ? nsub - 1 - p : p;
+            if (side && d == p) break;
+            if (tid == 0) {
+                dlist[nd] = d;
+                dbase[nd] = nblk;
+                for (int c = 0; c <= d; c++) {
+                    tab_c[nblk + c] = c;
+                    tab_d[nblk + c] = d;
+                }
+            }
+            nd++;
+            nblk += d + 1;
+        }
+    }
+    if (tid == 0) {
+        cluster_mbar_init(&rowbar[0], 1);
+        cluster_mbar_init(&rowbar[1], 1);
+        gaveup = 0;
+        best_score = -INFINITY;
+        best_len = 0;
+        best_vertex = 0;
+        if (rank == 0) redo[b] = 0;
+    }
+    __syncthreads();
+
+    // this warp's blocks, read once; anything but a finite number or -inf above the diagonal spoils the plain maximum
+    bool bad = false;
+    float eb[kClPerWarp][32];
+    int kc[kClPerWarp], kd[kClPerWarp];
+#pragma unroll
+    for (int q = 0; q < kClPerWarp; q++) {
+        const int k = warp + q * kClWarps;
+        kc[q] = -1;
+        kd[q] = -1;
+        if (k < nblk) {
+            kc[q] = tab_c[k];
+            kd[q] = tab_d[k];
+            const int j = 32 * kd[q] + lane;
+#pragma unroll
+            for (int r = 0; r < 32; r++) {
+                const int i = 32 * kc[q] + r;
+                float e = -INFINITY;
+                if (i < L && j < L && i < j) {
+                    e = __ldg(lk + (size_t)i * L + j);
+                    bad |= !(e < INFINITY);
+                }
+                eb[q][r] = e;
+            }
+        }
+    }
+    // on and below the diagonal everything must be -inf (rows dealt to the CTAs and warps in turn)
+    for (int i = rank * kClWarps + warp; i < L; i += nranks * kClWarps)
+        for (int j = lane; j <= i; j += 32) bad |= !(__ldg(lk + (size_t)i * L + j) == -INFINITY);
+    // step 0 (one transition out of vertex 0, :727-732): every CTA builds its own copy
+    const float l0 = joint ? logit[0] : 0.f;
+    for (int j = tid; j < Lp; j += kClThreads) {
+        float v = -INFINITY, lc = -INFINITY;
+        if (j < L) {
+            v = (lk[j] + l0) + logit[j];
+            lc = lk[(size_t)j * L + last];
+            bad |= !(v < INFINITY);
+            if (rank == 0 && max_length > 1) rows[j] = v;
+        }
+        row[j] = v;
+        row[Lp + j] = -INFINITY;
+        lastcol[j] = lc;
+    }
+    for (int x = tid; x < nd * 32; x += kClThreads) {
+        const int u = 32 * dlist[x >> 5] + (x & 31);
+        lgs[x] = u < L ? logit[u] : 0.f;
+    }
+    __syncthreads();
+    cluster_barrier();   // every CTA is set up (and the sentence's word in `redo` is cleared) before anyone writes
+    if (bad) atomicOr(redo + b, 1);
+
+    const uint32_t row_bytes = (uint32_t)nsub * 128u;
+    const int npairs = (nsub + 1) >> 1, nown = npairs < nranks ? npairs : nranks;
+    // the score of stopping after t+1 tokens (:747-754) is followed by the last warp of the first CTA
+    float bs_score = -INFINITY;
+    int bs_len = 0, bs_vertex = 0;
+    for (int t = 0; t < max_length && rank < nown; t++) {
+        const float *cur = row + (t & 1) * Lp;
+        float *nxt = row + ((t + 1) & 1) * Lp;
+        if (rank == 0 && warp == kClWarps - 1) {
+            float sv = -INFINITY;
+            int si = INT_MAX;
+            for (int j = lane; j < L; j += 32) vit_better(sv, si, cur[j] + lastcol[j], j);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, sv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, si, o);
+                vit_better(sv, si, ov, oi);
+            }
+            if (si == INT_MAX) si = 0;
+            const float sc = sv / powf((float)(t + 1), beta);
+            if (t == 0 || sc > bs_score) {   // first maximum over the lengths
+                bs_score = sc;
+                bs_len = t + 1;
+                bs_vertex = si;
+            }
+        }
+        if (t + 1 == max_length) break;
+        uint64_t *bar = &rowbar[(t + 1) & 1];
+        if (tid == 0) cluster_mbar_expect(bar, row_bytes);
+#pragma unroll
+        for (int q = 0; q < kClPerWarp; q++) {
+            if (kc[q] < 0) continue;   // warp-uniform
+            slot[(warp + q * kClWarps) * 32 + lane] = vit_block_max(cur + 32 * kc[q], eb[q]);
+        }
+        __syncthreads();
+        if (gaveup) break;   // (set during a wait, read after the barrier every thread passes next: the same for all)
+        if (warp < nd) {
+            const int d = dlist[warp], base = dbase[warp], u = 32 * d + lane;
+            float best = -INFINITY;
+            for (int c = 0; c <= d; c++) best = fmaxf(best, slot[(base + c) * 32 + lane]);
+            float v = joint ? best + lgs[warp * 32 + lane] : best;
+            if (u >= L) v = -INFINITY;
+            if (!(v < INFINITY)) atomicOr(redo + b, 1);   // +inf or NaN: the general kernel takes the sentence
+            for (int r = 0; r < nown; r++)
+                cluster_st_async_b32(cluster_map(nxt + u, r), __float_as_uint(v), cluster_map(bar, r));
+            if (u < L && t + 1 < max_length - 1) rows[(size_t)(t + 1) * L + u] = v;
+        }
+        const int s = t + 1;   // (this step's barrier has been through (s + 1) / 2 - 1 phases before this one)
+        if (!cluster_mbar_wait(bar, (uint32_t)((((s + 1) >> 1) + 1) & 1))) gaveup = 1;
+    }
+    if (rank == 0 && warp == kClWarps - 1 && lane == 0) {
+        best_score = bs_score;
+        best_len = bs_len;
+        best_vertex = bs_vertex;
+    }
+    __syncthreads();
+    if (gaveup && tid == 0) atomicOr(redo + b, 1);   // cannot happen
+    __threadfence();
+    cluster_barrier();   // every row is in the workspace; nobody leaves while a neighbour may still write here
+    if (rank != 0) return;
+    if (__ldcg(redo + b) != 0) return;   // the general kernel decodes this sentence
+
+    const int len = best_len;
+    int64_t *vert = out_vertices + (size_t)b * max_length;
+    {
+        int j = best_vertex;
+        for (int k = len - 1; k >= 0; k--) {
+            if (tid == 0) vert[k] = j;
+            if (k == 0) break;
+            const float *rowvals = rows + (size_t)(k - 1) * L;
+            unsigned long long key = 0ull;
+            for (int i = tid; i < L; i += kClThreads) {
+                float w = __ldcg(rowvals + i) + __ldg(lk + (size_t)i * L + j);
+                w += 0.0f;
+                const unsigned u = __float_as_uint(w);
+                const unsigned ord = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+                const unsigned long long kk = ((unsigned long long)ord << 32) | (0xffffffffu - (unsigned)i);
+                key = kk > key ? kk : key;
+            }
+            const unsigned hi = (unsigned)(key >> 32);
+            const unsigned mh = __reduce_max_sync(0xffffffffu, hi);
+            const unsigned ml = __reduce_max_sync(0xffffffffu, hi == mh ? (unsigned)key : 0u);
+            unsigned long long *slots = bt_slot[k & 1];
+            if (lane == 0) slots[warp] = ((unsigned long long)mh << 32) | ml;
+            __syncthreads();
+            const unsigned long long kw = lane < kClWarps ? slots[lane] : 0ull;
+            const unsigned kh = (unsigned)(kw >> 32);
+            const unsigned wh = __reduce_max_sync(0xffffffffu, kh);
+            const unsigned wl = __reduce_max_sync(0xffffffffu, kh == wh ? (unsigned)kw : 0u);
+            j = (int)(0xffffffffu - wl);
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int64_t *tok = out_tokens + (size_t)b * max_length;
+        const int64_t *tokens = tokens_all + (size_t)b * L;
+        for (int k = len; k < max_length; k++) vert[k] = -1;
+        // (the collapse of repeated / pad tokens, as in the general kernel)
+        int64_t lastt = tokens[vert[len - 1]];
+        int w = max_length - 1;
+        tok[w--] = lastt;
+        for (int k = len - 2; k >= 0; k--) {
+            const int64_t now = tokens[vert[k]];
+            if (now != pad && now != lastt) tok[w--] = now;
+            lastt = now;
+        }
+        const int n = max_length - 1 - w;
+        for (int k = 0; k < n; k++) tok[k] = tok[w + 1 + k];
+        for (int k = n; k < max_length; k++) tok[k] = pad;
+        out_length[b] = n;
+        out_score[b] = best_score;
+    }
+}
+
 }  // namespace dat
 
 extern "C" {
@@ -382,7 +663,10 @@ int dat_node_passing_prob(const float *links_square, float *node_pass, int bsz, 
 
 size_t dat_viterbi_decode_workspace_bytes(int bsz, int prelen, int max_length) {
     if (bsz <= 0 || prelen <= 0 || max_length <= 0) return 0;
-    return (size_t)bsz * (size_t)(max_length > 1 ? max_length - 1 : 1) * prelen * sizeof(int32_t);
+    // per sentence and step the back-pointers or the row's values, then one word per sentence (decoded by the
+    // cluster kernel / left to the general kernel)
+    return (size_t)bsz * (size_t)(max_length > 1 ? max_length - 1 : 1) * prelen * sizeof(int32_t) +
+           ((size_t)bsz + 64) * sizeof(int);
 }
 
 int dat_viterbi_decode(const float *links_square, const float *unreduced_logits,
@@ -399,14 +683,61 @@ int dat_viterbi_decode(const float *links_square, const float *unreduced_logits,
                     out_tokens && out_length && out_vertices && out_score,
                 DAT_ERR_BAD_ARG, "%s: null pointer", who);
     DAT_REQUIRE(prelen <= 4096, DAT_ERR_UNSUPPORTED, "%s: prelen=%d exceeds 4096", who, prelen);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t smem = (size_t)8 * ((prelen + 31) & ~31) * sizeof(float) + (((size_t)max_length + 15) & ~(size_t)15);
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(viterbi_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
             cudaSuccess)
         return check_launch(who);
-    viterbi_decode_kernel<<<(unsigned)bsz, kDecThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+    // graphs of up to 1024 vertices: a cluster per sentence with the matrix in its registers; the general kernel
+    // afterwards decodes only the sentences the cluster kernel left (matrices that are not clean and triangular)
+    int *redo = reinterpret_cast<int *>(static_cast<char *>(workspace) +
+                                        (size_t)bsz * (size_t)(max_length > 1 ? max_length - 1 : 1) * prelen * sizeof(int32_t));
+    const int *select = nullptr;
+    DeviceInfo di;
+    if (!device_info(&di)) return DAT_ERR_NO_DEVICE;
+    int cl_ranks = 0;
+    for (int r = 4; r <= kClMaxRanks && !cl_ranks; r *= 2)
+        if (cluster_fits(prelen, r)) cl_ranks = r;
+    const size_t csmem = viterbi_cluster_smem_bytes(prelen);
+    if (cl_ranks && csmem <= (size_t)di.max_smem_optin) {
+        bool ok = true;
+        if (csmem > 48 * 1024)
+            ok = cudaFuncSetAttribute(viterbi_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csmem) ==
+                 cudaSuccess;
+        if (ok && cl_ranks > 8)
+            ok = cudaFuncSetAttribute(viterbi_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) ==
+                 cudaSuccess;
+        cudaLaunchConfig_t ccfg = {};
+        cudaLaunchAttribute cattr[1];
+        ccfg.gridDim = dim3((unsigned)bsz * (unsigned)cl_ranks);
+        ccfg.blockDim = dim3(kClThreads);
+        ccfg.dynamicSmemBytes = csmem;
+        ccfg.stream = st;
+        cattr[0].id = cudaLaunchAttributeClusterDimension;
+        cattr[0].val.clusterDim.x = (unsigned)cl_ranks;
+        cattr[0].val.clusterDim.y = 1;
+        cattr[0].val.clusterDim.z = 1;
+        ccfg.attrs = cattr;
+        ccfg.numAttrs = 1;
+        int nclusters = 0;
+        if (ok) ok = cudaOccupancyMaxActiveClusters(&nclusters, viterbi_cluster_kernel, &ccfg) == cudaSuccess &&
+                     nclusters >= 1;
+        if (ok) {
+            if (cudaLaunchKernelEx(&ccfg, viterbi_cluster_kernel, links_square, unreduced_logits, unreduced_tokens,
+                                   output_length, static_cast<float *>(workspace), redo, out_tokens, out_length,
+                                   out_vertices, out_score, status, prelen, max_length, joint, beta,
+                                   pad_index) != cudaSuccess)
+                return check_launch("dat_viterbi_decode(cluster)");
+            if (int rc = check_launch("dat_viterbi_decode(cluster)")) return rc;
+            select = redo;
+        } else {
+            cudaGetLastError();   // not an error of the call: the general kernel decodes everything
+        }
+    }
+    viterbi_decode_kernel<<<(unsigned)bsz, kDecThreads, smem, st>>>(
         links_square, unreduced_logits, unreduced_tokens, output_length, static_cast<int32_t *>(workspace),
-        out_tokens, out_length, out_vertices, out_score, status, prelen, max_length, joint, beta, pad_index);
+        out_tokens, out_length, out_vertices, out_score, status, select, prelen, max_length, joint, beta, pad_index);
     return check_launch(who);
 }
 

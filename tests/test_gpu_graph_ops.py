@@ -314,6 +314,28 @@ def test_viterbi_decode_ties_take_the_first_index(joint):
     assert_rel(score.cpu().numpy(), rs, 1e-5, "score")
 
 
+def test_viterbi_decode_of_a_matrix_that_is_not_triangular():
+    """Finite entries on and below the diagonal: the cluster kernel (which holds only the upper triangle) must leave
+    such a sentence to the general kernel, which takes all L candidates; a triangular sentence in the same batch is
+    unaffected."""
+    gen = torch.Generator().manual_seed(29)
+    B, L, V = 3, 96, 13
+    ol = torch.tensor([96, 80, 96])
+    sq = workloads.band_to_square(workloads.make_links(B, L, ol, gen))
+    sq[1] = torch.randn(L, L, generator=gen) - 3.0          # dense
+    sq[2, 40, 10] = -0.25                                    # one transition backwards
+    logp = torch.log_softmax(torch.randn(B, L, V, generator=gen), -1)
+    ul, ut = logp.max(-1)
+    max_length = 24
+    toks, lens, verts, score = dag_viterbi_decode(sq.to(DEV), (ul.to(DEV), ut.to(DEV)), ol.to(DEV), max_length,
+                                                  joint=True, viterbibeta=1.0, pad_index=1)
+    rt, rl, rv, rs = oracle.viterbi_decode(sq.numpy(), ul.numpy(), ut.numpy(), ol.numpy(), max_length, joint=True,
+                                           beta=1.0, pad=1)
+    assert np.array_equal(verts.cpu().numpy(), rv)
+    assert np.array_equal(toks.cpu().numpy(), rt) and np.array_equal(lens.cpu().numpy(), rl)
+    assert_rel(score.cpu().numpy(), rs, 1e-5, "score")
+
+
 # ----------------------------------------------------------------------------- host upload
 def test_upload_links_moves_the_real_entries_and_the_ops_never_read_the_rest():
     """The band's padding is not transferred; the device copy keeps NaN there, and loss, gradients and
