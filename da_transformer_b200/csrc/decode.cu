@@ -15,7 +15,9 @@
 //     device (the reference back-traces in Python lists on the host).  A step whose sums cannot be NaN (triangular
 //     matrix without NaN or +inf, row without +inf or NaN) keeps its row's values instead of back-pointers; the
 //     back-trace re-evaluates the candidates of the vertices on the path.
-// One CTA per sentence; the matrix of a sentence (<= 4 MB) is served by L2 after its first read.
+// One CTA per sentence; the matrix of a sentence (<= 4 MB) is served by L2 after its first read.  Graphs of up to
+// 1024 vertices are decoded by a cluster per sentence with the matrix in its registers (viterbi_cluster_kernel);
+// the one-CTA kernel then only takes the sentences whose matrix is not what decoding builds.
 #include <climits>
 
 #include "cluster_util.cuh"
