@@ -137,7 +137,7 @@ def test_dag_loss_mean_matches_the_criterion_expression():
         work = work.masked_fill(invalid, 0)
         want = -(work / tl).mean()
         want.backward()
-        assert abs(float(loss) - float(want)) <= 1e-6 * max(1.0, abs(float(want)))
+        assert abs(float(loss.detach()) - float(want.detach())) <= 1e-6 * max(1.0, abs(float(want.detach())))
         assert torch.allclose(lr.grad, ref_in.grad, rtol=1e-6, atol=0)
         assert int(stats[3]) == int(bad.sum()) and int(stats[2]) == B
 
