@@ -314,6 +314,25 @@ def test_viterbi_decode_ties_take_the_first_index(joint):
     assert_rel(score.cpu().numpy(), rs, 1e-5, "score")
 
 
+@pytest.mark.parametrize("B,L,max_length", [(2, 1000, 40), (3, 520, 30), (2, 1300, 12)])
+def test_viterbi_decode_long_graphs(B, L, max_length):
+    """Graphs of 1000 and 520 vertices are decoded by clusters of 16 and 4 CTAs, 1300 vertices by the general kernel."""
+    gen = torch.Generator().manual_seed(31 + L)
+    ol = torch.randint(L // 2, L + 1, (B,), generator=gen)
+    ol[0] = L
+    sq = workloads.band_to_square(workloads.make_links(B, L, ol, gen))
+    logp = torch.log_softmax(torch.randn(B, L, 11, generator=gen) * 2, -1)
+    ul, ut = logp.max(-1)
+    toks, lens, verts, score = dag_viterbi_decode(sq.to(DEV), (ul.to(DEV), ut.to(DEV)), ol.to(DEV), max_length,
+                                                  joint=True, viterbibeta=1.0, pad_index=1)
+    rt, rl, rv, rs = oracle.viterbi_decode(sq.numpy(), ul.numpy(), ut.numpy(), ol.numpy(), max_length, joint=True,
+                                           beta=1.0, pad=1)
+    assert np.array_equal(verts.cpu().numpy(), rv)
+    assert np.array_equal(toks.cpu().numpy(), rt) and np.array_equal(lens.cpu().numpy(), rl)
+    assert_rel(score.cpu().numpy(), rs, 1e-5, "score")
+    assert last_status() == 0
+
+
 def test_viterbi_decode_of_a_matrix_that_is_not_triangular():
     """Finite entries on and below the diagonal: the cluster kernel (which holds only the upper triangle) must leave
     such a sentence to the general kernel, which takes all L candidates; a triangular sentence in the same batch is
